@@ -18,6 +18,9 @@ Beyond it:
   mixer still has the slots (with no tensors); they carry the per-request slot index.
 * A mixer that keeps one row per token instead of keys and values per head (a latent from which
   both are made) gets pages of such rows: [layer in group, 1, page, offset in page, width].
+* A mixer that keeps several things (pages and a state, or states of different shapes) names them
+  in a tuple; each member is kept as if it were a layer's only need (its key is (layer, index)),
+  and the layer's view holds the members' views in ``parts``.
 
 Storage layout of a group: [layer in group, 2 (keys, values), page, kv head,
 offset in page, head size]: the tokens of one page and one head are contiguous.
@@ -119,6 +122,7 @@ class LayerCache:
     slot_mapping: torch.Tensor | None = None  # int32 [tokens]: page * page_size + offset of each row
     state: torch.Tensor | None = None         # [slots, *shape] of a mixer with fixed-size state
     group: int = -1
+    parts: list | None = None                 # views of the members, for a mixer whose requirement is a tuple
 
 
 class CacheManager:
@@ -148,7 +152,15 @@ class CacheManager:
         self._high_water = {"blocks": 0, "used_tokens": 0, "sequences": 0}
 
         by_need: dict = {}
+        self.layer_members: dict[int, int] = {}     # layers whose requirement is a tuple: how many members
+        single: list = []                           # (key, need): a layer's only need, or one member of its tuple
         for layer, need in enumerate(requirements):
+            if isinstance(need, tuple):
+                self.layer_members[layer] = len(need)
+                single += [((layer, index), member) for index, member in enumerate(need)]
+            else:
+                single.append((layer, need))
+        for layer, need in single:
             if isinstance(need, (PagedKV, PagedLatent)):
                 group = by_need.get(need)
                 if group is None:
@@ -319,10 +331,14 @@ class CacheManager:
         request = self.requests[request_id]
         return request.tables_np[group_index][:len(request.tables[group_index])]
 
-    def layer_view(self, layer: int) -> LayerCache:
-        """The storage of ``layer`` (or of the layer whose cache it reads)."""
+    def layer_view(self, layer) -> LayerCache:
+        """The storage of ``layer`` (or of the layer whose cache it reads); for a layer with several needs, a view
+        whose ``parts`` are the members' views."""
         source = self.layer_source.get(layer, layer)
         view = LayerCache()
+        if source in self.layer_members:
+            view.parts = [self.layer_view((source, index)) for index in range(self.layer_members[source])]
+            return view
         if source in self.layer_group and source in self.groups[self.layer_group[source]].layer_slot:
             group_index = self.layer_group[source]
             group = self.groups[group_index]

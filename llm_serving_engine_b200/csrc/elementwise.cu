@@ -13,10 +13,10 @@ LSE_TL_DEFINE(lse_timeline_elementwise)
 LSE_CHECK_DEFINE(lse_check_elementwise)
 
 // ------------------------------------------------------------------ embedding
-// residual[t, :] = float(table[ids[t], :])
+// residual[t, :] = float(table[ids[t], :]) * scale
 template <typename T>
 __global__ void embedding_kernel(const T* __restrict__ table, const int* __restrict__ ids,
-                                 float* __restrict__ out, int hidden, int vocab, int copies) {
+                                 float* __restrict__ out, int hidden, int vocab, int copies, float scale) {
   LSE_TL_BEGIN(1)
   pdl_launch_dependents();
   pdl_wait();
@@ -30,24 +30,29 @@ __global__ void embedding_kernel(const T* __restrict__ table, const int* __restr
   }
   const T* src = table + (size_t)id * hidden;
   for (int i = threadIdx.x; i < hidden; i += blockDim.x) {
-    const float v = to_f32<T>(src[i]);
+    const float v = to_f32<T>(src[i]) * scale;
     for (int c = 0; c < copies; ++c) dst[(size_t)c * hidden + i] = v;
   }
   LSE_TL_MARK(3)
 }
 
-extern "C" int lse_embedding_copies(const void* table, int table_dtype, const int* ids, float* out,
-                                    int tokens, int hidden, int vocab, int copies, cudaStream_t stream) {
+extern "C" int lse_embedding_scaled(const void* table, int table_dtype, const int* ids, float* out, int tokens,
+                                    int hidden, int vocab, int copies, float scale, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (copies <= 0) return LSE_ERR_BAD_ARGUMENT;
   const int threads = hidden >= 1024 ? 256 : 128;
   if (table_dtype == LSE_DTYPE_F32)
-    lse_launch(embedding_kernel<float>, tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab, copies);
+    lse_launch(embedding_kernel<float>, tokens, threads, 0, stream, (const float*)table, ids, out, hidden, vocab, copies, scale);
   else if (table_dtype == LSE_DTYPE_BF16)
-    lse_launch(embedding_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab, copies);
+    lse_launch(embedding_kernel<__nv_bfloat16>, tokens, threads, 0, stream, (const __nv_bfloat16*)table, ids, out, hidden, vocab, copies, scale);
   else
     return LSE_ERR_BAD_ARGUMENT;
   LSE_LAUNCH_CHECK();
+}
+
+extern "C" int lse_embedding_copies(const void* table, int table_dtype, const int* ids, float* out,
+                                    int tokens, int hidden, int vocab, int copies, cudaStream_t stream) {
+  return lse_embedding_scaled(table, table_dtype, ids, out, tokens, hidden, vocab, copies, 1.0f, stream);
 }
 
 extern "C" int lse_embedding(const void* table, int table_dtype, const int* ids, float* out,
@@ -585,6 +590,7 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
 // FAST: the result is rounded to bfloat16, far more coarsely than the fast exponential and division err.
 template <int ACT, bool FAST>
 __device__ __forceinline__ float gate_act(float g) {
+  if (ACT == 2) return fmaxf(g, 0.f);
   if (ACT == 0) return FAST ? __fdividef(g, 1.0f + __expf(-g)) : g / (1.0f + expf(-g));
   const float inner = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
   if (FAST) return g - __fdividef(g, 1.0f + __expf(2.0f * inner));   // 0.5 g (1 + tanh x) = g - g / (1 + exp(2x))
@@ -711,13 +717,15 @@ extern "C" int lse_silu_mul(const void* gate_up, int in_dtype, int n_partials, l
   return gated_act_mul_launch<0>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, stream);
 }
 
-// activation: 0 = SiLU, 1 = the tanh form of GELU
+// activation: 0 = SiLU, 1 = the tanh form of GELU, 2 = ReLU
 extern "C" int lse_gated_act_mul(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,
                                  int out_dtype, int tokens, int inter, int activation, cudaStream_t stream) {
   if (activation == 0)
     return gated_act_mul_launch<0>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, stream);
   if (activation == 1)
     return gated_act_mul_launch<1>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, stream);
+  if (activation == 2)
+    return gated_act_mul_launch<2>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, stream);
   return LSE_ERR_BAD_ARGUMENT;
 }
 

@@ -38,14 +38,21 @@ __device__ __forceinline__ float la_act(float z, int act) { return act == 1 ? z 
 //     state at the chunk's start), outputs written, the state is not stored.
 // Chunks are what lets a long prompt use the whole GPU: a request's rows are walked in order only within a chunk.
 // OUTPUTS false: the pass that only builds a chunk's own state (phase 1) leaves the output's half of the work out.
-template <typename TD, int PARTS, bool OUTPUTS>
+//
+// GATED: the decay and the weight of the new outer product are numbers per token and head instead of one decay per head,
+//     S_t = keep[t, h] * S_(t-1) + take[t, h] * k_t v_t^T,
+// and the state has one more column, whose "value" is one for every token: it carries n_t = keep n_(t-1) + take k_t, so
+// that the output's last column is n_t . q_t (the normaliser of a gated matrix memory).  State and output rows then hold
+// vdim + 1 columns a head.  q is multiplied by q_scale in either form.
+template <typename TD, int PARTS, bool OUTPUTS, bool GATED>
 __global__ void __launch_bounds__(LA_THREADS, 4)     // four blocks an SM (measured faster than three blocks without the few spills)
 linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long long partial_stride, long long ld,
                              int q_off, int k_off, int v_off, const float* __restrict__ decay,
                              float* __restrict__ state, const int* __restrict__ segment_start,
                              const int* __restrict__ segment_slot, float* __restrict__ out, int heads, int dim,
                              int vdim, int act, int num_slots, int num_segments, int chunk_rows, int phase,
-                             float* __restrict__ chunk_state) {
+                             float* __restrict__ chunk_state, const float* __restrict__ token_keep,
+                             const float* __restrict__ token_take, float q_scale) {
   constexpr int CW = 32 / PARTS;
   constexpr int CB = 4 * CW;
   constexpr int PADDED = LA_DPT + 4;                // a part's 32 values, 16-byte aligned and four banks apart from the next part's
@@ -54,7 +61,9 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
   constexpr int QK_LOADS = LA_TT * PARTS * LA_DPT / LA_THREADS;   // values of q (and of k) a thread stages per tile
   constexpr int V_LOADS = (LA_TT * CB + LA_THREADS - 1) / LA_THREADS;
   __shared__ __align__(16) float q_s[LA_TT * QS], k_s[LA_TT * QS], v_s[LA_TT * CB];
+  __shared__ float keep_s[LA_TT];
   __shared__ int item[3];
+  const int vs = GATED ? vdim + 1 : vdim;     // columns of a head's state and of its output
   pdl_launch_dependents();
   pdl_wait();
   const int h = blockIdx.y, col0 = blockIdx.z * CB;
@@ -85,30 +94,31 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
   if (row1 <= row0) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int part = lane / CW, cb = warp * CW + lane % CW, col = col0 + cb;
-  const float dk = decay[h];
+  const float decay_h = GATED ? 1.f : decay[h];
   float* st = chunk_rows == 0
-      ? state + ((size_t)LSE_CHECKED(segment_slot[seg], 0, num_slots, 0, LSE_CHECK_ROW) * heads + h) * dim * vdim
-      : chunk_state + ((size_t)blockIdx.x * heads + h) * dim * vdim;
+      ? state + ((size_t)LSE_CHECKED(segment_slot[seg], 0, num_slots, 0, LSE_CHECK_ROW) * heads + h) * dim * vs
+      : chunk_state + ((size_t)blockIdx.x * heads + h) * dim * vs;
   const bool from_zero = chunk_rows > 0 && phase == 1;
   const bool store = !(chunk_rows > 0 && phase == 2);
   float s[LA_DPT];
 #pragma unroll
   for (int i = 0; i < LA_DPT; ++i) {
     const int d = part * LA_DPT + i;
-    s[i] = (!from_zero && d < dim && col < vdim) ? st[(size_t)d * vdim + col] : 0.f;
+    s[i] = (!from_zero && d < dim && col < vs) ? st[(size_t)d * vs + col] : 0.f;
   }
-  float qv[QK_LOADS], kv[QK_LOADS], vv_in[V_LOADS];
+  float qv[QK_LOADS], kv[QK_LOADS], vv_in[V_LOADS], take[QK_LOADS];
   auto fetch = [&](int base) {      // a tile's q, k and v into registers, all loads in flight together
     const int n = min(LA_TT, row1 - base);
 #pragma unroll
     for (int i = 0; i < QK_LOADS; ++i) {
       const int e = threadIdx.x + i * LA_THREADS;
       const int t = e / (PARTS * LA_DPT), d = e % (PARTS * LA_DPT);
-      qv[i] = kv[i] = 0.f;
+      qv[i] = kv[i] = take[i] = 0.f;
       if (t < n && d < dim) {
         const TD* row = proj + (size_t)(base + t) * ld + h * dim + d;
         qv[i] = la_load(row + q_off, n_partials, partial_stride);
         kv[i] = la_load(row + k_off, n_partials, partial_stride);
+        if (GATED) take[i] = token_take[(size_t)(base + t) * heads + h];
       }
     }
 #pragma unroll
@@ -118,6 +128,8 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
       vv_in[i] = 0.f;
       if (e < LA_TT * CB && t < n && col0 + c < vdim)
         vv_in[i] = la_load(proj + (size_t)(base + t) * ld + v_off + h * vdim + col0 + c, n_partials, partial_stride);
+      else if (GATED && e < LA_TT * CB && t < n && col0 + c == vdim)
+        vv_in[i] = 1.f;      // the normaliser's column
     }
   };
   fetch(row0);
@@ -129,13 +141,15 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
       const int e = threadIdx.x + i * LA_THREADS;
       const int t = e / (PARTS * LA_DPT), d = e % (PARTS * LA_DPT);
       const int at = t * QS + (d / LA_DPT) * PADDED + d % LA_DPT;
-      q_s[at] = la_act(qv[i], act);
-      k_s[at] = la_act(kv[i], act);
+      q_s[at] = la_act(qv[i], act) * q_scale;
+      k_s[at] = GATED ? la_act(kv[i], act) * take[i] : la_act(kv[i], act);
     }
+    if (GATED && threadIdx.x < LA_TT)
+      keep_s[threadIdx.x] = (int)threadIdx.x < n ? token_keep[(size_t)(base + threadIdx.x) * heads + h] : 1.f;
 #pragma unroll
     for (int i = 0; i < V_LOADS; ++i) {
       const int e = threadIdx.x + i * LA_THREADS;
-      if (e < LA_TT * CB) v_s[e] = la_act(vv_in[i], act);
+      if (e < LA_TT * CB) v_s[e] = (GATED && col0 + e % CB == vdim) ? vv_in[i] : la_act(vv_in[i], act);
     }
     __syncthreads();
     if (base + LA_TT < row1) fetch(base + LA_TT);    // the next tile travels while this one is worked on
@@ -143,6 +157,7 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
       const float4* qr = reinterpret_cast<const float4*>(q_s + t * QS + part * PADDED);
       const float4* kr = reinterpret_cast<const float4*>(k_s + t * QS + part * PADDED);
       const float vv = v_s[t * CB + cb];
+      const float dk = GATED ? keep_s[t] : decay_h;
       float o[4] = {0.f, 0.f, 0.f, 0.f};     // four short chains instead of one of 32 dependent additions
 #pragma unroll
       for (int i = 0; i < LA_DPT / 4; ++i) {
@@ -160,7 +175,7 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
         float total = (o[0] + o[1]) + (o[2] + o[3]);
 #pragma unroll
         for (int off = CW; off < 32; off <<= 1) total += __shfl_xor_sync(0xffffffffu, total, off);
-        if (part == 0 && col < vdim) out[(size_t)(base + t) * heads * vdim + h * vdim + col] = total;
+        if (part == 0 && col < vs) out[(size_t)(base + t) * heads * vs + h * vs + col] = total;
       }
     }
   }
@@ -168,7 +183,7 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
 #pragma unroll
     for (int i = 0; i < LA_DPT; ++i) {
       const int d = part * LA_DPT + i;
-      if (d < dim && col < vdim) st[(size_t)d * vdim + col] = s[i];
+      if (d < dim && col < vs) st[(size_t)d * vs + col] = s[i];
     }
   }
 }
@@ -216,6 +231,56 @@ linear_attention_carry_kernel(const float* __restrict__ decay, float* __restrict
   *slot = running;
 }
 
+// The carry for the gated form: a chunk's decay is the product of its tokens' keep factors.  A block owns 256 elements
+// of one head's state of one request; its warps first multiply up every chunk's factors (shared memory, one number a
+// chunk), then every thread carries its element from chunk to chunk as above.  vs = columns of the state.
+__global__ void __launch_bounds__(256)
+linear_attention_gated_carry_kernel(const float* __restrict__ token_keep, float* __restrict__ state,
+                                    const int* __restrict__ segment_start, const int* __restrict__ segment_slot,
+                                    float* __restrict__ chunk_state, int heads, int dim, int vs, int num_slots,
+                                    int chunk_rows) {
+  extern __shared__ float chunk_keep[];     // [chunks of this request]
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seg = blockIdx.z, h = blockIdx.y;
+  const int a = segment_start[seg], b = segment_start[seg + 1];
+  if (b <= a) return;
+  const int chunks = (b - a + chunk_rows - 1) / chunk_rows;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  for (int c = warp; c < chunks; c += 8) {
+    const int r0 = a + c * chunk_rows, r1 = min(b, r0 + chunk_rows);
+    float product = 1.f;
+    for (int r = r0 + lane; r < r1; r += 32) product *= token_keep[(size_t)r * heads + h];
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) product *= __shfl_xor_sync(0xffffffffu, product, o);
+    if (lane == 0) chunk_keep[c] = product;
+  }
+  __syncthreads();
+  const int per_head = dim * vs;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= per_head) return;
+  int before = 0;
+  for (int s = 0; s < seg; ++s) before += (segment_start[s + 1] - segment_start[s] + chunk_rows - 1) / chunk_rows;
+  const size_t per_state = (size_t)heads * per_head;
+  const size_t at = (size_t)h * per_head + e;
+  float* slot = state + (size_t)LSE_CHECKED(segment_slot[seg], 0, num_slots, 0, LSE_CHECK_ROW) * per_state + at;
+  float running = *slot;
+  float* own = chunk_state + (size_t)before * per_state + at;
+  for (int c0 = 0; c0 < chunks; c0 += 8) {
+    float mine[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) mine[i] = c0 + i < chunks ? own[(size_t)(c0 + i) * per_state] : 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (c0 + i < chunks) {
+        own[(size_t)(c0 + i) * per_state] = running;
+        running = fmaf(chunk_keep[c0 + i], running, mine[i]);
+      }
+    }
+  }
+  *slot = running;
+}
+
 // out[t] = o[t] / sqrt(mean(o[t]^2) + eps) * weight * sigmoid(g[t]); g: columns g_off .. g_off + n of proj.
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(256)
@@ -241,37 +306,48 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const TD* __restrict__ proj, i
 
 // chunk_rows == 0: one block row per request of the step (max_segments), empty requests leave at once.
 // chunk_rows > 0: three launches over chunks of chunk_rows rows; chunk_state holds max_chunks states
-// [heads][dim][vdim] (max_chunks >= tokens / chunk_rows + max_segments bounds the number of chunks).
-extern "C" int lse_linear_attention_scan(const void* proj, int proj_dtype, int n_partials, long long partial_stride,
-                                         long long ld, int q_off, int k_off, int v_off, const float* decay,
-                                         float* state, const int* segment_start, const int* segment_slot, float* out,
-                                         int max_segments, int heads, int dim, int vdim, int act, int num_slots,
-                                         int chunk_rows, float* chunk_state, int max_chunks, cudaStream_t stream) {
+// [heads][dim][columns] (max_chunks >= tokens / chunk_rows + max_segments bounds the number of chunks).
+// token_keep, token_take (float32 [tokens, heads], or both null): the gated form, whose states and outputs have
+// vdim + 1 columns a head; decay is not read then.
+template <bool GATED>
+static int linear_attention_scan_launch(const void* proj, int proj_dtype, int n_partials, long long partial_stride,
+                                        long long ld, int q_off, int k_off, int v_off, const float* decay,
+                                        float* state, const int* segment_start, const int* segment_slot, float* out,
+                                        int max_segments, int heads, int dim, int vdim, int act, int num_slots,
+                                        int chunk_rows, float* chunk_state, int max_chunks, const float* token_keep,
+                                        const float* token_take, float q_scale, cudaStream_t stream) {
   if (max_segments <= 0) return 0;
   if (heads <= 0 || dim <= 0 || vdim <= 0 || dim > 8 * LA_DPT || heads > 65535) return LSE_ERR_BAD_ARGUMENT;
   if (chunk_rows < 0 || (chunk_rows > 0 && (chunk_state == nullptr || max_chunks <= 0))) return LSE_ERR_BAD_ARGUMENT;
+  const int vs = GATED ? vdim + 1 : vdim;
   int parts = 1;
   while (parts * LA_DPT < dim) parts <<= 1;
 #define LSE_LA_CASE(TD, P)                                                                                       \
   {                                                                                                              \
     const int cb = 4 * (32 / P);                                                                                 \
-    dim3 grid(chunk_rows ? max_chunks : max_segments, heads, (vdim + cb - 1) / cb);                              \
+    dim3 grid(chunk_rows ? max_chunks : max_segments, heads, (vs + cb - 1) / cb);                                \
     for (int phase = 1; phase <= (chunk_rows ? 2 : 1); ++phase) {                                                \
       if (chunk_rows && phase == 1)                                                                              \
-        lse_launch(linear_attention_scan_kernel<TD, P, false>, grid, LA_THREADS, 0, stream, (const TD*)proj,     \
-                   n_partials, partial_stride, ld, q_off, k_off, v_off, decay, state, segment_start,             \
-                   segment_slot, out, heads, dim, vdim, act, num_slots, max_segments, chunk_rows, phase,         \
-                   chunk_state);                                                                                 \
+        lse_launch(linear_attention_scan_kernel<TD, P, false, GATED>, grid, LA_THREADS, 0, stream,               \
+                   (const TD*)proj, n_partials, partial_stride, ld, q_off, k_off, v_off, decay, state,           \
+                   segment_start, segment_slot, out, heads, dim, vdim, act, num_slots, max_segments, chunk_rows, \
+                   phase, chunk_state, token_keep, token_take, q_scale);                                         \
       else                                                                                                       \
-        lse_launch(linear_attention_scan_kernel<TD, P, true>, grid, LA_THREADS, 0, stream, (const TD*)proj,      \
-                   n_partials, partial_stride, ld, q_off, k_off, v_off, decay, state, segment_start,             \
-                   segment_slot, out, heads, dim, vdim, act, num_slots, max_segments, chunk_rows, phase,         \
-                   chunk_state);                                                                                 \
+        lse_launch(linear_attention_scan_kernel<TD, P, true, GATED>, grid, LA_THREADS, 0, stream,                \
+                   (const TD*)proj, n_partials, partial_stride, ld, q_off, k_off, v_off, decay, state,           \
+                   segment_start, segment_slot, out, heads, dim, vdim, act, num_slots, max_segments, chunk_rows, \
+                   phase, chunk_state, token_keep, token_take, q_scale);                                         \
       if (chunk_rows && phase == 1) {                                                                            \
-        const size_t per_state = (size_t)heads * dim * vdim;                                                     \
-        lse_launch(linear_attention_carry_kernel, dim3((unsigned)((per_state + 255) / 256), max_segments), 256,  \
-                   0, stream, decay, state, segment_start, segment_slot, chunk_state, heads, dim, vdim,          \
-                   num_slots, chunk_rows);                                                                       \
+        const size_t per_state = (size_t)heads * dim * vs;                                                       \
+        if (GATED)                                                                                               \
+          lse_launch(linear_attention_gated_carry_kernel, dim3((unsigned)((dim * vs + 255) / 256), heads,        \
+                                                               max_segments),                                   \
+                     256, sizeof(float) * (size_t)max_chunks, stream, token_keep, state, segment_start,          \
+                     segment_slot, chunk_state, heads, dim, vs, num_slots, chunk_rows);                          \
+        else                                                                                                     \
+          lse_launch(linear_attention_carry_kernel, dim3((unsigned)((per_state + 255) / 256), max_segments),     \
+                     256, 0, stream, decay, state, segment_start, segment_slot, chunk_state, heads, dim, vdim,   \
+                     num_slots, chunk_rows);                                                                     \
       }                                                                                                          \
     }                                                                                                            \
   }
@@ -288,6 +364,32 @@ extern "C" int lse_linear_attention_scan(const void* proj, int proj_dtype, int n
 #undef LSE_LA_PARTS
 #undef LSE_LA_CASE
   LSE_LAUNCH_CHECK();
+}
+
+extern "C" int lse_linear_attention_scan(const void* proj, int proj_dtype, int n_partials, long long partial_stride,
+                                         long long ld, int q_off, int k_off, int v_off, const float* decay,
+                                         float* state, const int* segment_start, const int* segment_slot, float* out,
+                                         int max_segments, int heads, int dim, int vdim, int act, int num_slots,
+                                         int chunk_rows, float* chunk_state, int max_chunks, cudaStream_t stream) {
+  return linear_attention_scan_launch<false>(proj, proj_dtype, n_partials, partial_stride, ld, q_off, k_off, v_off,
+                                             decay, state, segment_start, segment_slot, out, max_segments, heads, dim,
+                                             vdim, act, num_slots, chunk_rows, chunk_state, max_chunks, nullptr,
+                                             nullptr, 1.0f, stream);
+}
+
+extern "C" int lse_gated_linear_attention_scan(const void* proj, int proj_dtype, int n_partials,
+                                               long long partial_stride, long long ld, int q_off, int k_off, int v_off,
+                                               const float* token_keep, const float* token_take, float q_scale,
+                                               float* state, const int* segment_start, const int* segment_slot,
+                                               float* out, int max_segments, int heads, int dim, int vdim,
+                                               int num_slots, int chunk_rows, float* chunk_state, int max_chunks,
+                                               cudaStream_t stream) {
+  if (!token_keep || !token_take) return LSE_ERR_BAD_ARGUMENT;
+  if (max_chunks > 12000) return LSE_ERR_TOO_LARGE;      // a chunk's factor lives in shared memory during the carry
+  return linear_attention_scan_launch<true>(proj, proj_dtype, n_partials, partial_stride, ld, q_off, k_off, v_off,
+                                            nullptr, state, segment_start, segment_slot, out, max_segments, heads, dim,
+                                            vdim, 0, num_slots, chunk_rows, chunk_state, max_chunks, token_keep,
+                                            token_take, q_scale, stream);
 }
 
 extern "C" int lse_gated_rmsnorm(const float* o, const void* proj, int proj_dtype, int n_partials,

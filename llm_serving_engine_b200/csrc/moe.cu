@@ -31,7 +31,7 @@ __global__ void __launch_bounds__(ROUTE_THREADS)
 moe_route_kernel(const float* __restrict__ logits, int n_partials, long long partial_stride, int ld,
                  const float* __restrict__ correction, int has_shared_gate, float* __restrict__ expert_weights,
                  float* __restrict__ identity_weight, float* __restrict__ shared_gate, int* __restrict__ chosen_out,
-                 int tokens, int outputs, int identity, int top) {
+                 int tokens, int outputs, int identity, int top, const float* __restrict__ logit_bias, int over_chosen) {
   extern __shared__ float smem[];   // per warp: [outputs] scores, [outputs] choice scores
   pdl_launch_dependents();
   pdl_wait();
@@ -44,7 +44,7 @@ moe_route_kernel(const float* __restrict__ logits, int n_partials, long long par
   auto logit = [&](int e) {
     float sum = 0.f;
     for (int p = 0; p < n_partials; ++p) sum += row[(size_t)p * partial_stride + e];
-    return sum;
+    return (logit_bias && e < outputs) ? sum + logit_bias[e] : sum;
   };
   const int experts = outputs - identity;
   float top_z = -INFINITY;
@@ -55,13 +55,14 @@ moe_route_kernel(const float* __restrict__ logits, int n_partials, long long par
   for (int e = lane; e < outputs; e += 32) sum += expf(score[e] - top_z);
   sum = warp_sum(sum);
   for (int e = lane; e < outputs; e += 32) {
-    const float s = expf(score[e] - top_z) / sum;
+    // over_chosen: the logits themselves are compared, and the weights are exp(z - largest) over the sum of the chosen ones
+    const float s = over_chosen ? score[e] : expf(score[e] - top_z) / sum;
     score[e] = s;
     choice[e] = correction ? s + correction[e] : s;
     if (e < experts) expert_weights[(size_t)t * experts + e] = 0.f;
   }
   __syncwarp();
-  float identity_sum = 0.f;
+  float identity_sum = 0.f, chosen_sum = 0.f;
   for (int k = 0; k < top; ++k) {
     float best = -INFINITY;
     int best_e = 0x7fffffff;
@@ -80,13 +81,19 @@ moe_route_kernel(const float* __restrict__ logits, int n_partials, long long par
         for (int rest = k; rest < top; ++rest) chosen_out[(size_t)t * top + rest] = -1;
       break;
     }
+    const float weight = over_chosen ? expf(score[best_e] - top_z) : score[best_e];
+    chosen_sum += weight;
     if (lane == 0) {
       choice[best_e] = -INFINITY;
-      if (best_e < experts) expert_weights[(size_t)t * experts + best_e] = score[best_e];
+      if (best_e < experts) expert_weights[(size_t)t * experts + best_e] = weight;
       if (chosen_out) chosen_out[(size_t)t * top + k] = best_e;
     }
-    if (best_e >= experts) identity_sum += score[best_e];
+    if (best_e >= experts) identity_sum += weight;
     __syncwarp();
+  }
+  if (over_chosen) {     // the softmax over the chosen logits only
+    for (int e = lane; e < experts; e += 32) expert_weights[(size_t)t * experts + e] /= chosen_sum;
+    identity_sum /= chosen_sum;
   }
   if (lane == 0) identity_weight[t] = identity_sum;
 }
@@ -120,7 +127,7 @@ template <typename TI, typename TO>
 __global__ void moe_gated_act8_kernel(const TI* __restrict__ gate_up, int n_partials, long long partial_stride,
                                       const float* __restrict__ expert_weights, const float* __restrict__ shared_gate,
                                       TO* __restrict__ out, int experts, int ff, int shared_ff, float limit,
-                                      float shared_limit, const int* __restrict__ valid_rows) {
+                                      float shared_limit, const int* __restrict__ valid_rows, int kind) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -153,6 +160,15 @@ __global__ void moe_gated_act8_kernel(const TI* __restrict__ gate_up, int n_part
     for (int e = 0; e < 8; ++e) { g[e] += a[e]; u[e] += b[e]; }
   }
   const float lim = shared ? shared_limit : limit;
+  if (kind == 1) {      // out = c * silu(g) * u, nothing clamped
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+      const float gated = sizeof(TO) == 2 ? __fdividef(g[e], 1.0f + __expf(-g[e])) : g[e] / (1.0f + expf(-g[e]));
+      y[e] = c * (gated * u[e]);
+    }
+    moe_store8<TO>(dst, y);
+    return;
+  }
 #pragma unroll
   for (int e = 0; e < 8; ++e) {
     const float gc = fminf(g[e], lim), uc = fminf(fmaxf(u[e], -lim), lim);
@@ -167,7 +183,7 @@ template <typename TI, typename TO>
 __global__ void moe_gated_act_kernel(const TI* __restrict__ gate_up, int n_partials, long long partial_stride,
                                      const float* __restrict__ expert_weights, const float* __restrict__ shared_gate,
                                      TO* __restrict__ out, int experts, int ff, int shared_ff, float limit,
-                                     float shared_limit) {
+                                     float shared_limit, int kind) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x;
@@ -187,6 +203,7 @@ __global__ void moe_gated_act_kernel(const TI* __restrict__ gate_up, int n_parti
     g += to_f32<TI>(row[(size_t)p * partial_stride + gate_at]);
     u += to_f32<TI>(row[(size_t)p * partial_stride + up_at]);
   }
+  if (kind == 1) { *dst = from_f32<TO>(c * (g / (1.0f + expf(-g)) * u)); return; }
   const float lim = shared ? shared_limit : limit;
   g = fminf(g, lim);
   u = fminf(fmaxf(u, -lim), lim);
@@ -290,6 +307,11 @@ __global__ void moe_combine_kernel(const T* __restrict__ down, const int* __rest
 }
 }  // namespace
 
+extern "C" int lse_moe_route_biased(const float* logits, int n_partials, long long partial_stride, int ld,
+                                    const float* correction, int has_shared_gate, float* expert_weights,
+                                    float* identity_weight, float* shared_gate, int* chosen, int tokens, int outputs,
+                                    int identity, int top, const float* logit_bias, int over_chosen, cudaStream_t stream);
+
 // logits float32 [tokens, ld] or n_partials partial sums partial_stride apart: column e < outputs is router output e,
 // column `outputs` the shared expert's gate (has_shared_gate); correction float32 [outputs] or null.
 // expert_weights float32 [tokens, outputs - identity]; identity_weight, shared_gate float32 [tokens];
@@ -297,6 +319,17 @@ __global__ void moe_combine_kernel(const T* __restrict__ down, const int* __rest
 extern "C" int lse_moe_route(const float* logits, int n_partials, long long partial_stride, int ld, const float* correction,
                              int has_shared_gate, float* expert_weights, float* identity_weight, float* shared_gate,
                              int* chosen, int tokens, int outputs, int identity, int top, cudaStream_t stream) {
+  return lse_moe_route_biased(logits, n_partials, partial_stride, ld, correction, has_shared_gate, expert_weights,
+                              identity_weight, shared_gate, chosen, tokens, outputs, identity, top, nullptr, 0, stream);
+}
+
+// logit_bias float32 [outputs] or null: added to the router's logits.  over_chosen: the `top` largest logits are chosen
+// (plus correction, if any) and the weights are the softmax over the chosen logits only.
+extern "C" int lse_moe_route_biased(const float* logits, int n_partials, long long partial_stride, int ld,
+                                    const float* correction, int has_shared_gate, float* expert_weights,
+                                    float* identity_weight, float* shared_gate, int* chosen, int tokens, int outputs,
+                                    int identity, int top, const float* logit_bias, int over_chosen,
+                                    cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (outputs <= 0 || identity < 0 || identity > outputs || top <= 0 || n_partials < 1 ||
       ld < outputs + (has_shared_gate ? 1 : 0))
@@ -306,14 +339,29 @@ extern "C" int lse_moe_route(const float* logits, int n_partials, long long part
   const size_t smem = sizeof(float) * 2 * (size_t)outputs * warps;
   lse_launch(moe_route_kernel, (tokens + warps - 1) / warps, ROUTE_THREADS, smem, stream, logits, n_partials,
              partial_stride, ld, correction, has_shared_gate, expert_weights, identity_weight, shared_gate, chosen, tokens,
-             outputs, identity, top);
+             outputs, identity, top, logit_bias, over_chosen);
   LSE_LAUNCH_CHECK();
 }
+
+extern "C" int lse_moe_gated_act_kind(const void* gate_up, int in_dtype, int n_partials, long long partial_stride,
+                                      const float* expert_weights, const float* shared_gate, void* out, int out_dtype,
+                                      int tokens, int experts, int ff, int shared_ff, float limit, float shared_limit,
+                                      const int* valid_rows, int kind, cudaStream_t stream);
 
 extern "C" int lse_moe_gated_act(const void* gate_up, int in_dtype, int n_partials, long long partial_stride,
                                  const float* expert_weights, const float* shared_gate, void* out, int out_dtype,
                                  int tokens, int experts, int ff, int shared_ff, float limit, float shared_limit,
                                  const int* valid_rows, cudaStream_t stream) {
+  return lse_moe_gated_act_kind(gate_up, in_dtype, n_partials, partial_stride, expert_weights, shared_gate, out, out_dtype,
+                                tokens, experts, ff, shared_ff, limit, shared_limit, valid_rows, 0, stream);
+}
+
+// kind 0: out = c * g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit);
+// kind 1: out = c * silu(g) * u.
+extern "C" int lse_moe_gated_act_kind(const void* gate_up, int in_dtype, int n_partials, long long partial_stride,
+                                      const float* expert_weights, const float* shared_gate, void* out, int out_dtype,
+                                      int tokens, int experts, int ff, int shared_ff, float limit, float shared_limit,
+                                      const int* valid_rows, int kind, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   const int inter = experts * ff + shared_ff;
   if (inter <= 0 || n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
@@ -324,10 +372,10 @@ extern "C" int lse_moe_gated_act(const void* gate_up, int in_dtype, int n_partia
 #define LSE_MOE_ACT_CASE(TI, TO)                                                                                      \
   if (wide)                                                                                                           \
     lse_launch(moe_gated_act8_kernel<TI, TO>, grid, threads, 0, stream, (const TI*)gate_up, n_partials, partial_stride, \
-               expert_weights, shared_gate, (TO*)out, experts, ff, shared_ff, limit, shared_limit, valid_rows);       \
+               expert_weights, shared_gate, (TO*)out, experts, ff, shared_ff, limit, shared_limit, valid_rows, kind); \
   else                                                                                                                \
     lse_launch(moe_gated_act_kernel<TI, TO>, grid, threads, 0, stream, (const TI*)gate_up, n_partials, partial_stride,  \
-               expert_weights, shared_gate, (TO*)out, experts, ff, shared_ff, limit, shared_limit)
+               expert_weights, shared_gate, (TO*)out, experts, ff, shared_ff, limit, shared_limit, kind)
   if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) { LSE_MOE_ACT_CASE(float, float); }
   else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) { LSE_MOE_ACT_CASE(__nv_bfloat16, __nv_bfloat16); }
   else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) { LSE_MOE_ACT_CASE(float, __nv_bfloat16); }

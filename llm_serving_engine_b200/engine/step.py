@@ -313,14 +313,16 @@ class StepRunner:
         step.want_rows = dev[lay.want[0]:lay.want[1]]
         group_maps = [dev[lo:hi] for lo, hi in lay.maps]
         group_tables = [dev[lo:hi].view(lay.segments, lay.table_width) for lo, hi in lay.tables]
-        caches = []
-        for view in self._layer_views:
+        def bind(view: LayerCache) -> LayerCache:
             layer_cache = LayerCache(keys=view.keys, values=view.values, state=view.state, group=view.group)
             if view.group >= 0:
                 layer_cache.slot_mapping = group_maps[view.group]
                 layer_cache.block_tables = group_tables[view.group]
-            caches.append(layer_cache)
-        return step, caches
+            if view.parts is not None:     # a mixer with several needs: one view per need
+                layer_cache.parts = [bind(part) for part in view.parts]
+            return layer_cache
+
+        return step, [bind(view) for view in self._layer_views]
 
     def prepare(self, entries: list[StepEntry], validated: bool = False):
         """Reserve, pack and upload a step; returns ``(StepContext, [LayerCache per layer run])``."""

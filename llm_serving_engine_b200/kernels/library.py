@@ -107,6 +107,35 @@ _SIGNATURES = {
     "lse_attention_scored_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
                                 c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p, c_void_p, c_int,
                                 c_void_p, c_void_p, c_longlong, c_void_p],
+    "lse_embedding_scaled": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "lse_tanh_norm": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lse_gated_linear_attention_scan": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p,
+                                        c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                        c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "lse_mlstm_gates": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p, c_float,
+                        c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lse_mlstm_readout": [c_void_p, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p,
+                          c_int, c_int, c_int, c_int, c_float, c_void_p, c_void_p],
+    "lse_short_conv_act": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "lse_short_conv_state": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                             c_int, c_int, c_int, c_void_p],
+    "lse_conv_qk_norm_rope": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_float, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                              c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "lse_head_gate_scale": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_longlong, c_int, c_int, c_int, c_float,
+                            c_void_p, c_void_p],
+    "lse_ssm_step_sizes": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int,
+                           c_int, c_void_p],
+    "lse_selective_scan": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p,
+                           c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                           c_void_p, c_void_p, c_int, c_longlong, c_float, c_int, c_int, c_int, c_int, c_void_p],
+    "lse_moe_route_biased": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                             c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
+    "lse_moe_gated_act_kind": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                               c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p],
     "lse_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "lse_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p],
@@ -149,7 +178,7 @@ def register_signatures(signatures: dict) -> None:
 CHECK_READERS = ("lse_check_elementwise", "lse_check_attention_generic", "lse_check_attention_mma", "lse_check_attention_tc",
                  "lse_check_residual_streams", "lse_check_linear_attention", "lse_check_attention_latent",
                  "lse_check_attention_latent_mma", "lse_check_rowwise_postnorm", "lse_check_attention_scored",
-                 "lse_check_attention_scored_mma")
+                 "lse_check_attention_scored_mma", "lse_check_mlstm", "lse_check_short_conv", "lse_check_selective_scan")
 CHECK_KINDS = {1: "token id", 2: "cache slot", 3: "block-table entry", 4: "segment number", 5: "row index"}
 
 

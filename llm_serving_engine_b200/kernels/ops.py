@@ -45,15 +45,15 @@ def sm_count(device=None) -> int:
     return count
 
 
-def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, copies: int = 1) -> torch.Tensor:
-    """out[t] = float32(table[ids[t]]), ``copies`` times side by side; ids int32 [T], out float32 [T, copies * H]."""
+def embedding(table: torch.Tensor, ids: torch.Tensor, out: torch.Tensor, copies: int = 1, scale: float = 1.0) -> torch.Tensor:
+    """out[t] = float32(table[ids[t]]) * scale, ``copies`` times side by side; ids int32 [T], out float32 [T, copies * H]."""
     _need_cuda(table, ids, out)
     vocab, hidden = table.shape
     assert ids.dtype == torch.int32 and out.dtype == torch.float32 and table.is_contiguous()
     assert out.shape == (ids.shape[0], copies * hidden) and out.is_contiguous()
     lib = library.load()
-    check(lib.lse_embedding_copies(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
-                                   ids.shape[0], hidden, vocab, int(copies), _stream()), "embedding")
+    check(lib.lse_embedding_scaled(table.data_ptr(), dtype_code(table.dtype), ids.data_ptr(), out.data_ptr(),
+                                   ids.shape[0], hidden, vocab, int(copies), float(scale), _stream()), "embedding")
     return out
 
 
@@ -387,12 +387,12 @@ def attention_tc_status() -> int:
     return int(library.load().lse_attention_tc_status())
 
 
-GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1}
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu": 2}
 
 
 def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> torch.Tensor:
     """out[t, i] = act(gate_i) * up_i; ``gate_up`` is [T, 2I] (the row is [gate (I) | up (I)]) or a
-    float32 stack of partial sums [P, T, 2I]; ``activation``: "silu" or "gelu_tanh" (the tanh form of GELU)."""
+    float32 stack of partial sums [P, T, 2I]; ``activation``: "silu", "gelu_tanh" (the tanh form of GELU) or "relu"."""
     _need_cuda(gate_up, out)
     tokens, two_i = gate_up.shape[-2], gate_up.shape[-1]
     assert two_i % 2 == 0 and out.shape == (tokens, two_i // 2) and out.is_contiguous()
@@ -936,15 +936,18 @@ def head_mix_gate(wide: torch.Tensor, mix: torch.Tensor | None, gate_proj: torch
 
 # ------------------------------------------------------------------ mixture of experts
 def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, outputs: int, identity: int, top: int,
-              shared_gate: bool = False, chosen: torch.Tensor | None = None):
+              shared_gate: bool = False, chosen: torch.Tensor | None = None, logit_bias: torch.Tensor | None = None,
+              over_chosen: bool = False):
     """The router of a mixture of experts, in float32.  ``logits`` float32 [T, N] (or a stack of partial sums [P, T, N]):
     column e < ``outputs`` is router output e (the last ``identity`` of them identity experts), column ``outputs`` the
     pre-activation of the shared expert's gate when ``shared_gate``; further columns are padding.  Scores softmax(z)
     over the outputs, the ``top`` largest of score + ``correction`` chosen, weights the scores themselves.  Returns
     (expert_weights float32 [T, experts], zero where not chosen; identity_weight float32 [T], the chosen identity
     experts' weights added up; the shared gate float32 [T] = sigmoid of its column, or None).  ``chosen`` int32
-    [T, top] receives the choices."""
-    _need_cuda(logits, correction, chosen)
+    [T, top] receives the choices.  ``logit_bias`` (float32 [outputs]) is added to the logits.  ``over_chosen``: the
+    largest logits are chosen and the weights are the softmax over the chosen logits only."""
+    _need_cuda(logits, correction, chosen, logit_bias)
+    assert logit_bias is None or (logit_bias.dtype == torch.float32 and logit_bias.shape == (outputs,))
     logits, code, n_partials, stride, ld = _projection(logits)
     tokens = logits.shape[-2]
     assert code == F32 and logits.shape[-1] >= outputs + int(shared_gate)
@@ -953,31 +956,37 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, outputs: in
     expert_weights = torch.empty((tokens, outputs - identity), dtype=torch.float32, device=logits.device)
     identity_weight = torch.empty((tokens,), dtype=torch.float32, device=logits.device)
     gate = torch.empty((tokens,), dtype=torch.float32, device=logits.device) if shared_gate else None
-    check(library.load().lse_moe_route(logits.data_ptr(), n_partials, stride, ld, _ptr(correction), int(shared_gate),
-                                       expert_weights.data_ptr(), identity_weight.data_ptr(), _ptr(gate), _ptr(chosen),
-                                       tokens, int(outputs), int(identity), int(top), _stream()), "moe_route")
+    check(library.load().lse_moe_route_biased(logits.data_ptr(), n_partials, stride, ld, _ptr(correction),
+                                              int(shared_gate), expert_weights.data_ptr(), identity_weight.data_ptr(),
+                                              _ptr(gate), _ptr(chosen), tokens, int(outputs), int(identity), int(top),
+                                              _ptr(logit_bias), int(over_chosen), _stream()), "moe_route")
     return expert_weights, identity_weight, gate
+
+
+MOE_ACTIVATIONS = {"clamped_swish": 0, "silu": 1}
 
 
 def moe_gated_act(gate_up: torch.Tensor, expert_weights: torch.Tensor, shared_gate: torch.Tensor | None,
                   out: torch.Tensor, experts: int, ff: int, shared_ff: int, limit: float, shared_limit: float,
-                  valid_rows: torch.Tensor | None = None) -> torch.Tensor:
+                  valid_rows: torch.Tensor | None = None, activation: str = "clamped_swish") -> torch.Tensor:
     """out[t, i] = c * g * sigmoid(1.702 g) * (u + 1) with g = min(gate_i, limit), u = clamp(up_i, -limit, limit), over
     the columns of all experts side by side (``experts`` blocks of ``ff``, then ``shared_ff`` of the shared expert with
     its own limit); c is the token's weight of the column's expert (``shared_gate`` for the shared columns; 1 where
     the weights are None).  ``gate_up`` is [T, 2 I] (expert by expert [gate | up], then the shared expert's
     [gate | up]) or a float32 stack of partial sums.  ``valid_rows`` (int32, one number on the device): rows from it on
-    may be left alone (the unused end of a buffer grouped by expert)."""
+    may be left alone (the unused end of a buffer grouped by expert).  ``activation`` "silu": out = c * silu(g) * u with
+    nothing clamped."""
     _need_cuda(gate_up, expert_weights, shared_gate, out, valid_rows)
     tokens, inter = out.shape
     assert inter == experts * ff + shared_ff and out.is_contiguous() and gate_up.shape[-1] == 2 * inter
     gate_up, n_partials, stride = _partials(gate_up, tokens, 2 * inter)
     assert expert_weights is None or (expert_weights.dtype == torch.float32 and expert_weights.shape == (tokens, experts)
                                       and expert_weights.is_contiguous())
-    check(library.load().lse_moe_gated_act(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride,
-                                           _ptr(expert_weights), _ptr(shared_gate), out.data_ptr(),
-                                           dtype_code(out.dtype), tokens, experts, ff, shared_ff, float(limit),
-                                           float(shared_limit), _ptr(valid_rows), _stream()), "moe_gated_act")
+    check(library.load().lse_moe_gated_act_kind(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride,
+                                                _ptr(expert_weights), _ptr(shared_gate), out.data_ptr(),
+                                                dtype_code(out.dtype), tokens, experts, ff, shared_ff, float(limit),
+                                                float(shared_limit), _ptr(valid_rows),
+                                                MOE_ACTIVATIONS[activation], _stream()), "moe_gated_act")
     return out
 
 
@@ -1020,3 +1029,227 @@ def moe_combine(down: torch.Tensor, row_of: torch.Tensor, chosen: torch.Tensor, 
                                          tokens, x.shape[1], top, expert_weights.shape[1], int(accumulate), _stream()),
           "moe_combine")
     return y
+
+
+# ------------------------------------------------------------------ the tanh norm
+def tanh_norm(residual: torch.Tensor, delta: torch.Tensor | None, after, before, out: torch.Tensor | None,
+              rows: torch.Tensor | None = None, write_residual: bool = True) -> torch.Tensor | None:
+    """residual += after(delta); out = before(residual[rows]), with the tanh norm f(x) = tanh(alpha x) * w + b.
+    ``after`` and ``before`` are (alpha float32 [1], w float32 [H], b float32 [H]) or None (``after`` None: the output is
+    added as it is; ``before`` None with ``out`` None: only the sum).  residual float32 [T, H]; delta [T, H] or a float32
+    stack of partial sums; out [R, H] in float32 or bfloat16, R = len(rows) or T."""
+    _need_cuda(residual, delta, out, rows)
+    tokens, hidden = residual.shape
+    assert residual.dtype == torch.float32 and residual.is_contiguous()
+    delta, n_partials, stride = _partials(delta, tokens, hidden)
+    for triple in (after, before):
+        if triple is not None:
+            alpha, weight, bias = triple
+            assert alpha.dtype == weight.dtype == bias.dtype == torch.float32 and alpha.numel() == 1
+            assert weight.shape == (hidden,) and bias.shape == (hidden,)
+    n_rows = tokens if rows is None else rows.shape[0]
+    if out is not None:
+        assert before is not None and out.shape == (n_rows, hidden) and out.is_contiguous()
+    assert rows is None or rows.dtype == torch.int32
+    code = dtype_code(delta.dtype) if delta is not None else F32
+    a, b = after or (None, None, None), before or (None, None, None)
+    check(library.load().lse_tanh_norm(residual.data_ptr(), _ptr(delta), code, n_partials, stride, _ptr(a[0]), _ptr(a[1]),
+                                       _ptr(a[2]), _ptr(b[0]), _ptr(b[1]), _ptr(b[2]), _ptr(out),
+                                       dtype_code(out.dtype) if out is not None else F32, _ptr(rows), n_rows, hidden,
+                                       int(write_residual), _stream()), "tanh_norm")
+    return out
+
+
+# ------------------------------------------------------------------ matrix memory with exponential gates
+def mlstm_gates(proj: torch.Tensor, i_off: int, f_off: int, i_bias: torch.Tensor, f_bias: torch.Tensor, cap: float,
+                state_m: torch.Tensor, segment_start: torch.Tensor, segment_slot: torch.Tensor, heads: int):
+    """From the gates' pre-activations (columns i_off + h and f_off + h of ``proj``, + bias): i = cap tanh(z / cap),
+    f = logsigmoid(cap tanh(z / cap)), m_t = max(f_t + m_(t-1), i_t) along every request's rows from and into
+    ``state_m`` float32 [slots, heads].  Returns (keep, take, floor) float32 [T, heads]: exp(f_t + m_(t-1) - m_t),
+    exp(i_t - m_t), exp(-m_t)."""
+    _need_cuda(proj, i_bias, f_bias, state_m, segment_start, segment_slot)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = proj.shape[-2]
+    assert state_m.dtype == torch.float32 and state_m.is_contiguous() and state_m.shape[1:] == (heads,)
+    assert i_bias.dtype == f_bias.dtype == torch.float32 and i_bias.shape == f_bias.shape == (heads,)
+    segments = segment_slot.shape[0]
+    assert segment_start.dtype == segment_slot.dtype == torch.int32 and segment_start.shape[0] == segments + 1
+    keep, take, floor = (torch.empty((tokens, heads), dtype=torch.float32, device=proj.device) for _ in range(3))
+    check(library.load().lse_mlstm_gates(proj.data_ptr(), code, n_partials, stride, ld, int(i_off), int(f_off),
+                                         i_bias.data_ptr(), f_bias.data_ptr(), float(cap), state_m.data_ptr(),
+                                         segment_start.data_ptr(), segment_slot.data_ptr(), keep.data_ptr(),
+                                         take.data_ptr(), floor.data_ptr(), segments, heads, state_m.shape[0],
+                                         _stream()), "mlstm_gates")
+    return keep, take, floor
+
+
+def gated_linear_attention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, keep: torch.Tensor,
+                                take: torch.Tensor, q_scale: float, state: torch.Tensor, segment_start: torch.Tensor,
+                                segment_slot: torch.Tensor, out: torch.Tensor, heads: int, dim: int, vdim: int,
+                                chunked: bool | None = None) -> torch.Tensor:
+    """S_t = keep[t, h] S_(t-1) + take[t, h] k_t [v_t | 1]^T, out_t = S_t^T (q_scale q_t), over the rows of every request
+    in order, from and into ``state`` float32 [slots, heads, dim, vdim + 1] (the last column is the normaliser n, so
+    out's last column is n_t . q_t); out float32 [T, heads * (vdim + 1)].  ``chunked`` as for
+    :func:`linear_attention_scan`."""
+    _need_cuda(proj, keep, take, state, segment_start, segment_slot, out)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = proj.shape[-2]
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, dim, vdim + 1)
+    assert keep.dtype == take.dtype == torch.float32 and keep.shape == take.shape == (tokens, heads)
+    assert keep.is_contiguous() and take.is_contiguous()
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (tokens, heads * (vdim + 1))
+    segments = segment_slot.shape[0]
+    assert segment_start.dtype == segment_slot.dtype == torch.int32 and segment_start.shape[0] == segments + 1
+    chunk_rows, chunk_state, max_chunks = 0, None, 0
+    if chunked if chunked is not None else tokens >= LINEAR_ATTENTION_CHUNKED_FROM:
+        chunk_rows = LINEAR_ATTENTION_CHUNK
+        max_chunks = tokens // chunk_rows + segments
+        chunk_state = torch.empty((max_chunks, heads, dim, vdim + 1), dtype=torch.float32, device=out.device)
+    check(library.load().lse_gated_linear_attention_scan(
+        proj.data_ptr(), code, n_partials, stride, ld, int(q_off), int(k_off), int(v_off), keep.data_ptr(),
+        take.data_ptr(), float(q_scale), state.data_ptr(), segment_start.data_ptr(), segment_slot.data_ptr(),
+        out.data_ptr(), segments, heads, dim, vdim, state.shape[0], chunk_rows, _ptr(chunk_state), max_chunks, _stream()),
+        "gated_linear_attention_scan")
+    return out
+
+
+def mlstm_readout(read: torch.Tensor, floor: torch.Tensor, proj: torch.Tensor, g_off: int, weight: torch.Tensor,
+                  eps: float, out: torch.Tensor, heads: int, vdim: int,
+                  segment_of_token: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t, h, :] = rms(read[t, h, :vdim] / (max(|read[t, h, vdim]|, floor[t, h]) + 1e-6)) * weight * sigmoid(gate), the
+    root mean square taken per head; the gate's pre-activation is columns g_off .. of ``proj``."""
+    _need_cuda(read, floor, proj, weight, out, segment_of_token)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = out.shape[0]
+    assert read.dtype == floor.dtype == weight.dtype == torch.float32 and read.is_contiguous() and floor.is_contiguous()
+    assert read.shape == (tokens, heads * (vdim + 1)) and floor.shape == (tokens, heads) and weight.shape == (heads * vdim,)
+    assert out.shape == (tokens, heads * vdim) and out.is_contiguous()
+    check(library.load().lse_mlstm_readout(read.data_ptr(), floor.data_ptr(), proj.data_ptr(), code, n_partials, stride, ld,
+                                           int(g_off), weight.data_ptr(), out.data_ptr(), dtype_code(out.dtype), tokens,
+                                           heads, vdim, float(eps), _ptr(segment_of_token), _stream()), "mlstm_readout")
+    return out
+
+
+# ------------------------------------------------------------------ short convolutions and what follows them
+def short_conv_act(proj: torch.Tensor, off: int, weight: torch.Tensor, bias: torch.Tensor | None, state: torch.Tensor,
+                   step, out: torch.Tensor, activation: str = "none") -> torch.Tensor:
+    """out[t, c] = act(sum_j weight[c, j] u_(t - taps + 1 + j)[c] + bias[c]) where u are columns off .. off + C of
+    ``proj`` along the request's rows and, before this step's rows, the request's window in ``state`` float32
+    [slots, taps - 1, C].  weight float32 [C, taps]; ``step``: the step's context; ``activation`` "none" or "silu"."""
+    _need_cuda(proj, weight, bias, state, out)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens, channels = out.shape
+    taps = weight.shape[1]
+    assert weight.dtype == torch.float32 and weight.shape == (channels, taps) and weight.is_contiguous()
+    assert bias is None or (bias.dtype == torch.float32 and bias.shape == (channels,))
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (taps - 1, channels)
+    assert out.is_contiguous() and proj.shape[-2] == tokens
+    check(library.load().lse_short_conv_act(proj.data_ptr(), code, n_partials, stride, ld, int(off), weight.data_ptr(),
+                                            _ptr(bias), state.data_ptr(), step.segment_of_token.data_ptr(),
+                                            step.segment_start.data_ptr(), step.segment_state_slot.data_ptr(),
+                                            out.data_ptr(), dtype_code(out.dtype), tokens, channels, taps,
+                                            {"none": 0, "silu": 1}[activation], state.shape[0],
+                                            step.segment_state_slot.shape[0], _stream()), "short_conv_act")
+    return out
+
+
+def short_conv_state(proj: torch.Tensor, off: int, channels: int, taps: int, state: torch.Tensor, step) -> None:
+    """Move every request's window in ``state`` (float32 [slots, taps - 1, channels]) on by the step's rows: afterwards it
+    holds the request's last taps - 1 inputs.  Launch it after the kernels that read the old window."""
+    _need_cuda(proj, state)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (taps - 1, channels)
+    check(library.load().lse_short_conv_state(proj.data_ptr(), code, n_partials, stride, ld, int(off), state.data_ptr(),
+                                              step.segment_start.data_ptr(), step.segment_state_slot.data_ptr(),
+                                              step.segment_state_slot.shape[0], channels, taps, state.shape[0], _stream()),
+          "short_conv_state")
+
+
+def conv_qk_norm_rope(proj: torch.Tensor, off: int, g_off: int, weight: torch.Tensor, state: torch.Tensor,
+                      q_norm: torch.Tensor, k_norm: torch.Tensor, eps: float, freq: torch.Tensor, rot_factor: float,
+                      step, slot_mapping: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor,
+                      gate_out: torch.Tensor | None, n_q: int, n_kv: int, dk: int, dv: int) -> None:
+    """Columns off .. of ``proj`` are [q (n_q dk) | k (n_kv dk) | v (n_kv dv)]; each passes its short convolution
+    (``weight`` float32 [channels, taps], windows in ``state``); q and k are RMS-normed over their whole width
+    (``q_norm`` [n_q dk], ``k_norm`` [n_kv dk]) and the first 2 len(freq) values of every head rotated (value i with
+    i + len(freq); angle position * freq[i], freq float64; cosine and sine times ``rot_factor``); q goes to ``q_out``
+    [T, n_q, dk], k and v into the row's place in the pages.  ``gate_out`` float32 [T, n_q] receives the sigmoid of
+    columns g_off .. g_off + n_q."""
+    _need_cuda(proj, weight, state, q_norm, k_norm, freq, slot_mapping, q_out, k_cache, v_cache, gate_out)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = q_out.shape[0]
+    channels, taps = (n_q + n_kv) * dk + n_kv * dv, weight.shape[1]
+    assert weight.dtype == torch.float32 and weight.shape == (channels, taps) and weight.is_contiguous()
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (taps - 1, channels)
+    assert q_norm.dtype == k_norm.dtype == torch.float32 and q_norm.shape == (n_q * dk,) and k_norm.shape == (n_kv * dk,)
+    assert freq.dtype == torch.float64 and freq.is_contiguous() and 2 * freq.shape[0] <= dk
+    assert q_out.shape == (tokens, n_q, dk) and q_out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert k_cache.dtype == v_cache.dtype == q_out.dtype and k_cache.shape[1] == n_kv and k_cache.shape[3] == dk
+    assert v_cache.shape[3] == dv and v_cache.shape[:3] == k_cache.shape[:3]
+    assert gate_out is None or (gate_out.dtype == torch.float32 and gate_out.shape == (tokens, n_q) and gate_out.is_contiguous())
+    assert slot_mapping.dtype == torch.int32 and slot_mapping.shape[0] >= tokens
+    check(library.load().lse_conv_qk_norm_rope(
+        proj.data_ptr(), code, n_partials, stride, ld, int(off), int(g_off), weight.data_ptr(), state.data_ptr(),
+        q_norm.data_ptr(), k_norm.data_ptr(), float(eps), freq.data_ptr(), float(rot_factor), 2 * freq.shape[0],
+        step.positions.data_ptr(), step.segment_of_token.data_ptr(), step.segment_start.data_ptr(),
+        step.segment_state_slot.data_ptr(), slot_mapping.data_ptr(), q_out.data_ptr(), k_cache.data_ptr(),
+        v_cache.data_ptr(), dtype_code(q_out.dtype), _ptr(gate_out), tokens, n_q, n_kv, dk, dv, taps, k_cache.shape[2],
+        k_cache.shape[0], state.shape[0], step.segment_state_slot.shape[0], _stream()), "conv_qk_norm_rope")
+
+
+def head_gate_scale(attended: torch.Tensor, gate: torch.Tensor | None, out: torch.Tensor, scale: float,
+                    segment_of_token: torch.Tensor | None = None) -> torch.Tensor:
+    """out[t, h * dv + j] = attended[t, h, j] * gate[t, h] * scale; ``out`` [T, heads * dv] may be a column range of a
+    wider tensor (rows strided)."""
+    _need_cuda(attended, gate, out, segment_of_token)
+    tokens, heads, dv = attended.shape
+    assert attended.is_contiguous() and out.shape == (tokens, heads * dv) and out.stride(1) == 1
+    assert gate is None or (gate.dtype == torch.float32 and gate.shape == (tokens, heads) and gate.is_contiguous())
+    check(library.load().lse_head_gate_scale(attended.data_ptr(), dtype_code(attended.dtype), _ptr(gate), out.data_ptr(),
+                                             dtype_code(out.dtype), out.stride(0), tokens, heads, dv, float(scale),
+                                             _ptr(segment_of_token), _stream()), "head_gate_scale")
+    return out
+
+
+# ------------------------------------------------------------------ selective state-space scan
+def ssm_step_sizes(low: torch.Tensor, weight_t: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
+    """dt float32 [T, C] = softplus(low[:, :rank] @ weight_t + bias); ``low``: a projection's rows (or partial sums),
+    ``weight_t`` float32 [rank, C]."""
+    _need_cuda(low, weight_t, bias)
+    low, code, n_partials, stride, ld = _projection(low)
+    tokens = low.shape[-2]
+    rank, channels = weight_t.shape
+    assert weight_t.dtype == bias.dtype == torch.float32 and weight_t.is_contiguous() and bias.shape == (channels,)
+    assert low.shape[-1] >= rank
+    dt = torch.empty((tokens, channels), dtype=torch.float32, device=low.device)
+    check(library.load().lse_ssm_step_sizes(low.data_ptr(), code, n_partials, stride, ld, weight_t.data_ptr(),
+                                            bias.data_ptr(), dt.data_ptr(), tokens, channels, rank, _stream()),
+          "ssm_step_sizes")
+    return dt
+
+
+def selective_scan(x: torch.Tensor, dt: torch.Tensor, proj: torch.Tensor, z_off: int, low: torch.Tensor, b_off: int,
+                   c_off: int, a_log: torch.Tensor, skip: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor,
+                   scale: float = 1.0) -> torch.Tensor:
+    """S[c, n] <- exp(dt[c] A[c, n]) S[c, n] + dt[c] x[c] B[n];  y[c] = sum_n S[c, n] C[n] + skip[c] x[c];
+    out[t, c] = y[c] silu(z[c]) * scale, over the rows of every request in order, from and into ``state`` float32
+    [slots, C, N].  A = -exp(a_log) (float32 [C, N]); B and C are columns b_off .. and c_off .. of ``low``, z columns
+    z_off .. of ``proj`` (each a projection's rows or partial sums); x [T, C] in the compute dtype, dt float32 [T, C];
+    ``out`` [T, C] may be a column range of a wider tensor."""
+    _need_cuda(x, dt, proj, low, a_log, skip, state, out)
+    proj, p_code, p_partials, p_stride, p_ld = _projection(proj)
+    low, l_code, l_partials, l_stride, l_ld = _projection(low)
+    tokens, channels = x.shape
+    states = a_log.shape[1]
+    assert x.is_contiguous() and dt.dtype == torch.float32 and dt.is_contiguous() and dt.shape == x.shape
+    assert a_log.dtype == skip.dtype == torch.float32 and a_log.shape == (channels, states) and a_log.is_contiguous()
+    assert skip.shape == (channels,)
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (channels, states)
+    assert out.shape == (tokens, channels) and out.stride(1) == 1 and out.dtype == x.dtype
+    check(library.load().lse_selective_scan(
+        x.data_ptr(), dtype_code(x.dtype), dt.data_ptr(), proj.data_ptr(), p_code, p_partials, p_stride, p_ld, int(z_off),
+        low.data_ptr(), l_code, l_partials, l_stride, l_ld, int(b_off), int(c_off), a_log.data_ptr(), skip.data_ptr(),
+        state.data_ptr(), step.segment_start.data_ptr(), step.segment_state_slot.data_ptr(), out.data_ptr(),
+        dtype_code(out.dtype), out.stride(0), float(scale), step.segment_state_slot.shape[0], channels, states,
+        state.shape[0], _stream()), "selective_scan")
+    return out

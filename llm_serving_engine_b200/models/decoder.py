@@ -166,16 +166,17 @@ class DecoderModel:
         tokens = step.num_tokens
         copies = self.spec.residual_streams
         residual = torch.empty((tokens, copies * self.spec.hidden_size), dtype=torch.float32, device=self.device)
-        if self.position_table is not None or self.spec.embedding_scale != 1.0:
-            if copies != 1 or self.position_table is None:
-                raise ops.KernelError("a scaled embedding comes with a position table and one copy of the residual")
+        if self.position_table is not None:
+            if copies != 1:
+                raise ops.KernelError("a position table comes with one copy of the residual")
             hidden = residual if self.dtype == torch.float32 else torch.empty_like(residual, dtype=self.dtype)
             ops.embedding_positions(self.embedding, self.position_table, step.token_ids, step.positions,
                                     self.spec.embedding_scale, residual, None if hidden is residual else hidden)
             stream = ResidualStream(residual, copies=copies)
             stream.hidden = hidden
         else:
-            ops.embedding(self.embedding, step.token_ids, residual, copies)   # every copy starts as the embedding
+            # every copy starts as the embedding
+            ops.embedding(self.embedding, step.token_ids, residual, copies, scale=self.spec.embedding_scale)
             stream = ResidualStream(residual, copies=copies)
         for position, index in enumerate(self.spec.order):   # caches run along the order
             self.blocks[index].forward(stream, step, caches[position])

@@ -1,4 +1,5 @@
-from . import attention, block, latent_attention, linear_attention, mlp, moe, norm, normed_attention, rope  # noqa: F401  (register the built-in parts)
+from . import (attention, block, branches, latent_attention, linear_attention, mlp, mlstm, moe, norm,  # noqa: F401
+               normed_attention, rope)   # (register the built-in parts)
 from .base import (BLOCKS, FEED_FORWARDS, MIXERS, NORMS, POSITION_ENCODINGS, Block, BuildContext,
                    FeedForward, Mixer, Norm, PagedKV, PagedLatent, Part, PositionEncoding, RequestState,
                    ResidualStream, register_block, register_feed_forward, register_mixer,

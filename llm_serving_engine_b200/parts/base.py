@@ -13,7 +13,8 @@ configuration), ``weights`` (its own tensors, by their local names) and a
                        that the next norm adds up; ``reduce_partials`` gives [T, H]),
                        reading and writing its layer's cache; ``cache_requirement``
                        says what it needs (pages of keys and values, or a
-                       fixed-size state per request, or nothing)
+                       fixed-size state per request, or nothing, or a tuple of
+                       several such needs: pages and a state, two states)
 * ``FeedForward``:     ``forward(x) -> y``, row-local
 * ``Block``:           the arrangement of the four in a layer:
                        ``forward(stream, step, cache)``
@@ -84,7 +85,7 @@ class ResidualStream:
     applies all of it (``Norm.forward``)."""
 
     __slots__ = ("residual", "delta", "copies", "delta_mult", "delta_scale", "mix", "write", "read", "hidden",
-                 "delta_bias", "delta_row_scale")
+                 "delta_bias", "delta_row_scale", "delta_norm")
 
     def __init__(self, residual: torch.Tensor, delta: torch.Tensor | None = None, copies: int = 1) -> None:
         self.residual = residual
@@ -101,6 +102,7 @@ class ResidualStream:
         self.hidden = None
         self.delta_bias = None
         self.delta_row_scale = None   # float32 [T] c: c_t times the branch's input row belongs to the pending output too
+        self.delta_norm = None        # a Norm that the pending output passes before it is added (a layer that norms after a branch too)
 
     @property
     def plain(self) -> bool:
@@ -140,7 +142,9 @@ class Mixer(Part):
 
     @classmethod
     def cache_requirement(cls, params: dict[str, Any], hidden_size: int):
-        """``PagedKV``, ``RequestState`` or ``None``."""
+        """``PagedKV``, ``PagedLatent``, ``RequestState`` or ``None``; or a tuple of these, when the mixer keeps several
+        things (pages and a state, two states of different shapes): ``forward`` then finds them, in the tuple's
+        order, in ``cache.parts``."""
         return None
 
     def forward(self, x: torch.Tensor, step, cache) -> torch.Tensor:
@@ -151,6 +155,27 @@ class Mixer(Part):
         launches (``segment_counts``: tokens of each request in the step).  Steps with different signatures
         are captured in CUDA graphs of their own; ``forward`` must choose by the same rule."""
         return ()
+
+
+def cache_needs(requirement) -> tuple:
+    """A mixer's cache requirement as a tuple of single needs (empty for none)."""
+    if requirement is None:
+        return ()
+    return tuple(requirement) if isinstance(requirement, tuple) else (requirement,)
+
+
+def cache_for(cache, needs: int, first: int = 0):
+    """What a mixer with ``needs`` single needs gets when its needs are members ``first`` .. of a larger tuple (a mixer
+    built from several): the member itself for one need, a view whose ``parts`` are the members for several, None for
+    none."""
+    if needs == 0:
+        return None
+    members = cache.parts[first:first + needs]
+    if needs == 1:
+        return members[0]
+    view = type(cache)()
+    view.parts = members
+    return view
 
 
 class FeedForward(Part):

@@ -4,7 +4,7 @@ from __future__ import annotations
 import torch
 
 from ..weights.tensor_spec import TensorSpec
-from .base import Block, ResidualStream, register_block
+from .base import NORMS, Block, ResidualStream, register_block
 
 
 @register_block("prenorm_residual")
@@ -93,3 +93,47 @@ class PostNormResidualBlock(Block):
             stream.delta = self.feed_forward.forward(x)
             stream.delta_row_scale = self.feed_forward.row_scale
             self.feed_forward_norm.forward(stream)
+
+
+@register_block("sandwich_residual")
+class SandwichResidualBlock(Block):
+    """h = h + after1(mixer(before1(h))); h = h + after2(feed_forward(before2(h))): a norm before and a norm after every
+    branch.  The norms before are the layer's ``mixer_norm`` and ``feed_forward_norm``; the norms after belong to the
+    arrangement: params ``after_norm`` ({"kind", "params"}: a registered norm, built once per branch) and
+    ``after_prefixes`` ({"mixer": ..., "feed_forward": ...}: their tensors' prefixes after the layer's).  A branch's
+    output stays pending in the stream together with its norm (``stream.delta_norm``); the next norm before applies
+    both in its one launch.  A layer may have no feed-forward."""
+
+    graph_safe = True
+
+    def __init__(self, params, mixer_norm, mixer, feed_forward_norm, feed_forward, weights=None, ctx=None) -> None:
+        super().__init__(params, mixer_norm, mixer, feed_forward_norm, feed_forward)
+        weights = weights or {}
+        spec, prefixes = params["after_norm"], params["after_prefixes"]
+        cls = NORMS.get(spec["kind"])
+
+        def build(prefix: str):
+            local = {name[len(prefix):]: tensor for name, tensor in weights.items() if name.startswith(prefix)}
+            return cls(spec["params"], local, ctx)
+
+        self.mixer_after = build(prefixes["mixer"])
+        self.feed_forward_after = build(prefixes["feed_forward"]) if feed_forward is not None else None
+
+    @classmethod
+    def expected_tensors(cls, params, hidden_size):
+        spec, prefixes = params["after_norm"], params["after_prefixes"]
+        declared = NORMS.get(spec["kind"]).expected_tensors(spec["params"], hidden_size)
+        roles = ("mixer", "feed_forward") if params.get("feed_forward", True) else ("mixer",)
+        return {prefixes[role] + local: tensor for role in roles for local, tensor in declared.items()}
+
+    def parts(self) -> list:
+        return super().parts() + [part for part in (self.mixer_after, self.feed_forward_after) if part is not None]
+
+    def forward(self, stream: ResidualStream, step, cache) -> None:
+        x = self.mixer_norm.forward(stream)
+        stream.delta = self.mixer.forward(x, step, cache)
+        stream.delta_norm = self.mixer_after
+        if self.feed_forward is not None:
+            x = self.feed_forward_norm.forward(stream)
+            stream.delta = self.feed_forward.forward(x)
+            stream.delta_norm = self.feed_forward_after

@@ -1,0 +1,252 @@
+"""Mixers that can run side by side on one input: a grouped-query attention behind short convolutions, a selective
+state-space scan, and the mixer that sums several such branches with a weight each."""
+from __future__ import annotations
+
+import torch
+
+from ..kernels import ops
+from ..weights.tensor_spec import TensorSpec
+from .base import MIXERS, Mixer, PagedKV, RequestState, cache_for, cache_needs, register_mixer
+from .latent_attention import rotary_frequencies
+from .linear import linear_partials
+from .mlstm import input_projection
+
+
+class BranchMixer(Mixer):
+    """A mixer of the form  y = W_out inner(W_in x):  its input product and its output product can be shared with other
+    mixers that read the same x (their input matrices stacked into one product, their output matrices side by side,
+    so that the sum of the branches is one product too).  A subclass sets ``in_weight`` [n_in, H] and ``out_weight``
+    [H, n_mid] and implements ``inner(proj, offset, step, cache, out, scale)``: its columns of the stacked
+    projection start at ``offset``; it writes ``scale`` times its activations into ``out`` [T, n_mid], which may be
+    a column range of a wider tensor."""
+
+    in_weight: torch.Tensor
+    out_weight: torch.Tensor
+
+    def inner(self, proj, offset: int, step, cache, out: torch.Tensor, scale: float) -> None:
+        raise NotImplementedError
+
+    def forward(self, x, step, cache):
+        proj = input_projection(x, self.in_weight)
+        mid = torch.empty((x.shape[0], self.out_weight.shape[1]), dtype=x.dtype, device=x.device)
+        self.inner(proj, 0, step, cache, mid, 1.0)
+        return linear_partials(mid, self.out_weight)
+
+
+_ATTENTION_NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o", "q_norm": "q.norm", "k_norm": "k.norm",
+                    "conv_suffix": ".conv"}
+
+
+@register_mixer("conv_rotary_attention")
+class ConvRotaryAttention(BranchMixer):
+    """params: ``heads``, ``kv_heads`` (query head h uses key/value head h // (heads / kv_heads)), ``dim`` (of a head's
+    query and key), ``vdim`` (of its value), ``conv`` (taps of the short causal convolution that q, k and v each
+    pass, per channel, straight after their projection; 1: none), ``eps`` (of the norms), ``rot`` ({base, dims,
+    scaling}: the first ``dims`` values of every head are rotated, value i paired with i + dims / 2; see
+    ``rotary_frequencies`` for ``scaling``), ``scale`` (on the scores), ``gate`` (head h's output times
+    sigmoid(w_g,h x)), ``tensor_names``.
+
+    After the convolutions q and k are RMS-normed over their whole width (all heads at once, weights of that width),
+    then rotated; the softmax is the ordinary causal one.  Kept per request: pages of keys and values, and the last
+    ``conv - 1`` projected rows [q | k | v] (float32), so that a step may start anywhere.
+
+    One kernel does convolution, norms, rotation, the page write and the gates' sigmoid; the attention itself is the
+    engine's paged attention for keys and values of any sizes (tensor cores for bfloat16 shapes that it takes)."""
+
+    graph_safe = True
+
+    def __init__(self, params, weights, ctx) -> None:
+        super().__init__(params, weights, ctx)
+        p = params
+        self.n_q, self.n_kv = int(p["heads"]), int(p["kv_heads"])
+        self.dk, self.dv, self.taps = int(p["dim"]), int(p["vdim"]), int(p.get("conv", 1))
+        self.scale, self.eps = float(p["scale"]), float(p["eps"])
+        if self.n_q % self.n_kv:
+            raise ops.KernelError(f"attention: {self.n_q} query heads do not divide into {self.n_kv} groups")
+        rot = p.get("rot") or {"dims": 0, "base": 1.0}
+        if int(rot["dims"]) % 2 or int(rot["dims"]) > self.dk:
+            raise ops.KernelError(f"attention: {rot['dims']} rotated values of {self.dk}")
+        freq, self.rot_factor = rotary_frequencies(rot) if int(rot["dims"]) else (torch.zeros(0, dtype=torch.float64), 1.0)
+        self.freq = freq.to(torch.float64).contiguous().to(ctx.device)
+        names = {**_ATTENTION_NAMES, **p.get("tensor_names", {})}
+        stacked = [weights[names[role]] for role in ("q", "k", "v")]
+        self.channels = sum(w.shape[0] for w in stacked)
+        self.has_gate = bool(p.get("gate", False))
+        if self.has_gate:
+            stacked.append(weights[names["gate"]])
+        self.in_weight = torch.cat(stacked, dim=0).contiguous()
+        if self.taps > 1:
+            self.conv_weight = torch.cat([weights[names[role] + names["conv_suffix"]].to(torch.float32)
+                                          for role in ("q", "k", "v")], dim=0).contiguous()
+        else:
+            self.conv_weight = torch.ones((self.channels, 1), dtype=torch.float32, device=ctx.device)
+        self.q_norm = weights[names["q_norm"]].to(torch.float32).contiguous()
+        self.k_norm = weights[names["k_norm"]].to(torch.float32).contiguous()
+        self.out_weight = weights[names["out"]].contiguous()
+
+    @classmethod
+    def expected_tensors(cls, params, hidden_size):
+        p = params
+        n_q, n_kv, dk, dv, taps = int(p["heads"]), int(p["kv_heads"]), int(p["dim"]), int(p["vdim"]), int(p.get("conv", 1))
+        names = {**_ATTENTION_NAMES, **p.get("tensor_names", {})}
+        out = {names["q"]: TensorSpec((n_q * dk, hidden_size)), names["k"]: TensorSpec((n_kv * dk, hidden_size)),
+               names["v"]: TensorSpec((n_kv * dv, hidden_size)), names["out"]: TensorSpec((hidden_size, n_q * dv)),
+               names["q_norm"]: TensorSpec((n_q * dk,), "norm"), names["k_norm"]: TensorSpec((n_kv * dk,), "norm")}
+        if taps > 1:
+            for role in ("q", "k", "v"):
+                out[names[role] + names["conv_suffix"]] = TensorSpec((out[names[role]].shape[0], taps), "filter")
+        if p.get("gate", False):
+            out[names["gate"]] = TensorSpec((n_q, hidden_size))
+        return out
+
+    @classmethod
+    def cache_requirement(cls, params, hidden_size):
+        n_q, n_kv, dk, dv = int(params["heads"]), int(params["kv_heads"]), int(params["dim"]), int(params["vdim"])
+        taps = int(params.get("conv", 1))
+        pages = PagedKV(n_kv, dk, 0, 0 if dv == dk else dv)
+        return (pages, RequestState((max(taps - 1, 0), (n_q + n_kv) * dk + n_kv * dv), "float32"))
+
+    def inner(self, proj, offset, step, cache, out, scale):
+        pages, window = cache.parts[0], cache.parts[1].state
+        tokens = out.shape[0]
+        q = torch.empty((tokens, self.n_q, self.dk), dtype=out.dtype, device=out.device)
+        gate = torch.empty((tokens, self.n_q), dtype=torch.float32, device=out.device) if self.has_gate else None
+        ops.conv_qk_norm_rope(proj, offset, offset + self.channels, self.conv_weight, window, self.q_norm, self.k_norm,
+                              self.eps, self.freq, self.rot_factor, step, pages.slot_mapping, q, pages.keys, pages.values,
+                              gate, self.n_q, self.n_kv, self.dk, self.dv)
+        if self.taps > 1:
+            ops.short_conv_state(proj, offset, self.channels, self.taps, window, step)
+        attended = torch.empty((tokens, self.n_q, self.dv), dtype=out.dtype, device=out.device)
+        ops.attention_scored(q, pages.keys, pages.values, attended, pages.block_tables, step.segment_of_token,
+                             step.positions, self.scale, segment_start=step.segment_start,
+                             segment_first_position=step.segment_first_position)
+        ops.head_gate_scale(attended, gate, out, scale, step.segment_of_token)
+
+
+_SSM_NAMES = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "x": "x", "dt": "dt", "dt_bias": "dt.b",
+              "a_log": "A_log", "skip": "D", "out": "o"}
+
+
+@register_mixer("selective_state_space")
+class SelectiveStateSpace(BranchMixer):
+    """params: ``inner`` (channels), ``state`` (states per channel), ``dt_rank``, ``conv`` (taps), ``tensor_names``.
+
+    W_in x = [u | z]; u passes a short causal convolution per channel (with bias) and SiLU; W_x u = [low (dt_rank) |
+    B (state) | C (state)]; dt = softplus(W_dt low + b_dt) per channel; A = -exp(A_log);
+        S[c, n] <- exp(dt_c A[c, n]) S[c, n] + dt_c u_c B_n;      y_c = sum_n S[c, n] C_n + D_c u_c;
+    the output is W_out (y * silu(z)).  Kept per request, in float32: S [inner, state] and the last ``conv - 1`` rows
+    of u before the convolution.  Step sizes, decays, B, C and the state are float32."""
+
+    graph_safe = True
+
+    def __init__(self, params, weights, ctx) -> None:
+        super().__init__(params, weights, ctx)
+        p = params
+        self.channels, self.states, self.rank, self.taps = int(p["inner"]), int(p["state"]), int(p["dt_rank"]), int(p["conv"])
+        names = {**_SSM_NAMES, **p.get("tensor_names", {})}
+        self.in_weight = weights[names["in"]].contiguous()
+        self.conv_weight = weights[names["conv"]].to(torch.float32).contiguous()
+        self.conv_bias = weights[names["conv_bias"]].to(torch.float32).contiguous()
+        low = weights[names["x"]]
+        pad = -low.shape[0] % 16       # whole tiles of the few-rows product
+        self.low_weight = (torch.cat([low, low.new_zeros((pad, low.shape[1]))]) if pad else low).contiguous()
+        self.dt_weight_t = weights[names["dt"]].to(torch.float32).t().contiguous()      # [rank, channels]
+        self.dt_bias = weights[names["dt_bias"]].to(torch.float32).contiguous()
+        self.a_log = weights[names["a_log"]].to(torch.float32).contiguous()
+        self.skip = weights[names["skip"]].to(torch.float32).contiguous()
+        self.out_weight = weights[names["out"]].contiguous()
+
+    @classmethod
+    def expected_tensors(cls, params, hidden_size):
+        p = params
+        inner, states, rank, taps = int(p["inner"]), int(p["state"]), int(p["dt_rank"]), int(p["conv"])
+        names = {**_SSM_NAMES, **p.get("tensor_names", {})}
+        return {names["in"]: TensorSpec((2 * inner, hidden_size)), names["conv"]: TensorSpec((inner, taps), "filter"),
+                names["conv_bias"]: TensorSpec((inner,), "bias"), names["x"]: TensorSpec((rank + 2 * states, inner)),
+                names["dt"]: TensorSpec((inner, rank)), names["dt_bias"]: TensorSpec((inner,), "bias"),
+                names["a_log"]: TensorSpec((inner, states), "positive"), names["skip"]: TensorSpec((inner,), "norm"),
+                names["out"]: TensorSpec((hidden_size, inner))}
+
+    @classmethod
+    def cache_requirement(cls, params, hidden_size):
+        inner, states, taps = int(params["inner"]), int(params["state"]), int(params["conv"])
+        return (RequestState((inner, states), "float32"), RequestState((max(taps - 1, 0), inner), "float32"))
+
+    def inner(self, proj, offset, step, cache, out, scale):
+        state, window = cache.parts[0].state, cache.parts[1].state
+        tokens = out.shape[0]
+        u = torch.empty((tokens, self.channels), dtype=out.dtype, device=out.device)
+        ops.short_conv_act(proj, offset, self.conv_weight, self.conv_bias, window, step, u, "silu")
+        if self.taps > 1:
+            ops.short_conv_state(proj, offset, self.channels, self.taps, window, step)
+        low = input_projection(u, self.low_weight)
+        dt = ops.ssm_step_sizes(low, self.dt_weight_t, self.dt_bias)
+        ops.selective_scan(u, dt, proj, offset + self.channels, low, self.rank, self.rank + self.states, self.a_log,
+                           self.skip, state, step, out, scale)
+
+
+@register_mixer("parallel_mixers")
+class ParallelMixers(Mixer):
+    """params: ``branches``: a list of {"kind" (a registered mixer of the ``BranchMixer`` form), "params", "prefix" (of
+    its tensors after this part's), "scale"}.
+
+    y = sum_b scale_b * branch_b(x): every branch reads the same x.  The branches' input matrices are stacked into
+    one product and their output matrices laid side by side, each branch writing scale_b times its activations into
+    its columns of one tensor, so that the weighted sum is the one output product.  Each branch keeps what it
+    keeps alone; this part's requirement is the branches' needs in a row."""
+
+    graph_safe = True
+
+    def __init__(self, params, weights, ctx) -> None:
+        super().__init__(params, weights, ctx)
+        self.branches, self.scales, self.needs = [], [], []
+        for branch in params["branches"]:
+            cls = MIXERS.get(branch["kind"])
+            if not issubclass(cls, BranchMixer):
+                raise ops.KernelError(f"parallel mixers: {branch['kind']!r} cannot share its products with a sibling")
+            prefix = branch["prefix"]
+            local = {name[len(prefix):]: tensor for name, tensor in weights.items() if name.startswith(prefix)}
+            self.branches.append(cls(branch["params"], local, ctx))
+            self.scales.append(float(branch.get("scale", 1.0)))
+            self.needs.append(len(cache_needs(cls.cache_requirement(branch["params"], ctx.hidden_size))))
+        if not all(branch.graph_safe for branch in self.branches):
+            self.graph_safe = False
+        self.in_weight = torch.cat([branch.in_weight for branch in self.branches], dim=0).contiguous()
+        pad = -self.in_weight.shape[0] % 16
+        if pad:
+            self.in_weight = torch.cat([self.in_weight, self.in_weight.new_zeros((pad, self.in_weight.shape[1]))]).contiguous()
+        self.out_weight = torch.cat([branch.out_weight for branch in self.branches], dim=1).contiguous()
+        self.in_offsets, self.mid_offsets = [0], [0]
+        for branch in self.branches:
+            self.in_offsets.append(self.in_offsets[-1] + branch.in_weight.shape[0])
+            self.mid_offsets.append(self.mid_offsets[-1] + branch.out_weight.shape[1])
+            branch.in_weight = branch.out_weight = None      # held once, stacked
+
+    @classmethod
+    def expected_tensors(cls, params, hidden_size):
+        out = {}
+        for branch in params["branches"]:
+            declared = MIXERS.get(branch["kind"]).expected_tensors(branch["params"], hidden_size)
+            out.update({branch["prefix"] + local: tensor for local, tensor in declared.items()})
+        return out
+
+    @classmethod
+    def cache_requirement(cls, params, hidden_size):
+        needs = ()
+        for branch in params["branches"]:
+            needs += cache_needs(MIXERS.get(branch["kind"]).cache_requirement(branch["params"], hidden_size))
+        return needs or None
+
+    def launch_signature(self, segment_counts):
+        return tuple(answer for branch in self.branches for answer in branch.launch_signature(segment_counts))
+
+    def forward(self, x, step, cache):
+        proj = input_projection(x, self.in_weight)
+        mid = torch.empty((x.shape[0], self.mid_offsets[-1]), dtype=x.dtype, device=x.device)
+        first = 0
+        for index, branch in enumerate(self.branches):
+            view = mid[:, self.mid_offsets[index]:self.mid_offsets[index + 1]]
+            branch.inner(proj, self.in_offsets[index], step, cache_for(cache, self.needs[index], first), view,
+                         self.scales[index])
+            first += self.needs[index]
+        return linear_partials(mid, self.out_weight)

@@ -15,8 +15,8 @@ from .linear import linear, linear_partials, SKINNY_MAX_ROWS
 # every row: with few rows the experts' weights are what the step waits for, and nearly all of them are read either way.
 GROUPED_FROM_ROWS = int(os.environ.get("LSE_MOE_GROUPED_FROM", "128"))
 
-_DEFAULT_NAMES = {"router": "router", "correction": "correction", "expert": "e{index}.", "shared": "shared.",
-                  "gate": "gate", "up": "up", "down": "down", "shared_gate": "sg"}
+_DEFAULT_NAMES = {"router": "router", "router_bias": "router.b", "correction": "correction", "expert": "e{index}.",
+                  "shared": "shared.", "gate": "gate", "up": "up", "down": "down", "shared_gate": "sg"}
 
 
 @register_feed_forward("clamped_moe")
@@ -24,7 +24,10 @@ class ClampedMoE(FeedForward):
     """params: ``experts``, ``identity`` (the router's last ``identity`` outputs stand for experts whose output is the
     input itself), ``top``, ``ff`` and ``limit`` of an expert, ``correction`` (a learned vector added to the scores for
     the choice only; default true), ``shared`` ({"ff", "limit"} or None: an expert that every token uses, times
-    sigmoid(w_sg . x)), ``tensor_names``.
+    sigmoid(w_sg . x)), ``router_bias`` (the router's logits have a bias vector; default false), ``weights``
+    ("softmax_all", the default below, or "softmax_chosen": the ``top`` largest logits are chosen and the weights are
+    the softmax over the chosen logits only), ``activation`` ("clamped_swish", the default below, or "silu":
+    y = W_down (silu(W_gate x) * (W_up x)), nothing clamped, ``limit`` not read), ``tensor_names``.
 
     Expert: g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit), y = W_down (g sigmoid(1.702 g) (u + 1)).
     Router: s = softmax(W_router x) over all outputs, in float32; the ``top`` outputs with the largest s + correction
@@ -47,7 +50,13 @@ class ClampedMoE(FeedForward):
         super().__init__(params, weights, ctx)
         p = params
         self.experts, self.identity, self.top = int(p["experts"]), int(p.get("identity", 0)), int(p["top"])
-        self.ff, self.limit = int(p["ff"]), float(p["limit"])
+        self.activation = p.get("activation", "clamped_swish")
+        if self.activation not in ops.MOE_ACTIVATIONS:
+            raise ops.KernelError(f"mixture of experts: activation {self.activation!r} is not one of {sorted(ops.MOE_ACTIVATIONS)}")
+        if p.get("weights", "softmax_all") not in ("softmax_all", "softmax_chosen"):
+            raise ops.KernelError(f"mixture of experts: weights {p.get('weights')!r} must be softmax_all or softmax_chosen")
+        self.over_chosen = p.get("weights", "softmax_all") == "softmax_chosen"
+        self.ff, self.limit = int(p["ff"]), float(p.get("limit", 0.0))
         shared = p.get("shared")
         self.shared_ff = int(shared["ff"]) if shared else 0
         self.shared_limit = float(shared["limit"]) if shared else 0.0
@@ -68,6 +77,7 @@ class ClampedMoE(FeedForward):
             rows.append(torch.zeros((pad, rows[0].shape[1]), dtype=rows[0].dtype, device=rows[0].device))
         self.router = torch.cat(rows, dim=0).contiguous()
         self.correction = weights[names["correction"]].float().contiguous() if p.get("correction", True) else None
+        self.router_bias = weights[names["router_bias"]].float().contiguous() if p.get("router_bias", False) else None
         self.row_scale = None    # after forward: float32 [T] c_t, when c_t x_t is still to be added to the output
         # views of the stacked matrices for the grouped product: [experts, width, 2 ff] and [experts, ff, width]
         self._grouped_gate_up = self._grouped_down = None
@@ -86,6 +96,8 @@ class ClampedMoE(FeedForward):
         out = {names["router"]: TensorSpec((experts + identity, hidden_size))}
         if p.get("correction", True):
             out[names["correction"]] = TensorSpec((experts + identity,), "bias")
+        if p.get("router_bias", False):
+            out[names["router_bias"]] = TensorSpec((experts + identity,), "bias")
         sized = [(names["expert"].format(index=index), ff) for index in range(experts)]
         if p.get("shared"):
             sized.append((names["shared"], int(p["shared"]["ff"])))
@@ -114,7 +126,8 @@ class ClampedMoE(FeedForward):
         ops.moe_gather_rows(x, row_of, grouped)
         gate_up = torch._grouped_mm(grouped, self._grouped_gate_up, offs=offsets)     # rows beyond the last range stay as they are
         act = torch.empty((rows, self.ff), dtype=x.dtype, device=x.device)
-        ops.moe_gated_act(gate_up, None, None, act, 1, self.ff, 0, self.limit, 0.0, valid_rows=offsets[-1:])
+        ops.moe_gated_act(gate_up, None, None, act, 1, self.ff, 0, self.limit, 0.0, valid_rows=offsets[-1:],
+                          activation=self.activation)
         down = torch._grouped_mm(act, self._grouped_down, offs=offsets)
         out = y if y is not None else torch.empty((tokens, width), dtype=torch.float32, device=x.device)
         return ops.moe_combine(down, row_of, chosen, expert_weights, identity_weight if self.identity else None, x, out,
@@ -129,7 +142,8 @@ class ClampedMoE(FeedForward):
         else:
             logits = linear(x, self.router, out_dtype=torch.float32)
         return ops.moe_route(logits, self.correction, self.outputs, self.identity, self.top,
-                             shared_gate=self.shared_ff > 0, chosen=chosen)
+                             shared_gate=self.shared_ff > 0, chosen=chosen, logit_bias=self.router_bias,
+                             over_chosen=self.over_chosen)
 
     def forward(self, x):
         tokens = x.shape[0]
@@ -141,7 +155,7 @@ class ClampedMoE(FeedForward):
             gate_up = linear_partials(x, self.gate_up_weight)
             act = torch.empty((tokens, self.inter), dtype=x.dtype, device=x.device)
             ops.moe_gated_act(gate_up, expert_weights, shared_gate, act, self.experts, self.ff, self.shared_ff,
-                              self.limit, self.shared_limit)
+                              self.limit, self.shared_limit, activation=self.activation)
             if x.dtype == torch.bfloat16 and tokens > SKINNY_MAX_ROWS:
                 y = linear(act, self.down_weight, out_dtype=torch.float32)
             else:
@@ -151,3 +165,6 @@ class ClampedMoE(FeedForward):
         if self.identity:
             self.row_scale = identity_weight     # the identity experts' share w_t x_t: the norm that adds the output adds it
         return y
+
+
+register_feed_forward("routed_experts", ClampedMoE)   # the same part under a name that does not say which activation

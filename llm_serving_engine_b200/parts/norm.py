@@ -77,3 +77,54 @@ class RMSNormAfterSum(Norm):
                                self.weight, self.eps, copy)
         stream.delta = stream.delta_bias = stream.delta_row_scale = None
         return stream.hidden
+
+
+@register_norm("dynamic_tanh")
+class DynamicTanh(Norm):
+    """params: ``weight_name`` (default "weight"), ``bias_name`` (default: the weight's name + ".b"), ``alpha_name``
+    (default: the weight's name + ".alpha").
+
+    A norm without statistics: y = tanh(alpha x) * w + b with a learned scalar alpha, elementwise, in float32.
+    As a layer's norm it adds the pending branch output to the float32 residual first; when the stream says that
+    the output passes a norm of its own before it is added (``stream.delta_norm``, a norm of this kind: a layer that
+    norms before and after each branch), the same launch applies that too:
+        residual += after(delta);   returns before(residual)."""
+
+    graph_safe = True
+
+    def __init__(self, params, weights, ctx) -> None:
+        super().__init__(params, weights, ctx)
+        weight, bias, alpha = self._names(params)
+        self.weight = weights[weight].to(torch.float32).contiguous()
+        self.bias = weights[bias].to(torch.float32).contiguous()
+        self.alpha = weights[alpha].to(torch.float32).reshape(1).contiguous()
+
+    @staticmethod
+    def _names(params) -> tuple[str, str, str]:
+        weight = params.get("weight_name", "weight")
+        return weight, params.get("bias_name", weight + ".b"), params.get("alpha_name", weight + ".alpha")
+
+    @classmethod
+    def expected_tensors(cls, params, hidden_size):
+        weight, bias, alpha = cls._names(params)
+        return {weight: TensorSpec((hidden_size,), "norm"), bias: TensorSpec((hidden_size,), "bias"),
+                alpha: TensorSpec((), "norm")}
+
+    @property
+    def triple(self):
+        return self.alpha, self.weight, self.bias
+
+    def forward(self, stream: ResidualStream, rows: torch.Tensor | None = None) -> torch.Tensor:
+        if not stream.plain:
+            raise ops.KernelError("dynamic_tanh: one copy of the residual, branch outputs added as they are")
+        after = stream.delta_norm
+        if after is not None and not isinstance(after, DynamicTanh):
+            raise ops.KernelError("dynamic_tanh: the norm of a branch's output must be of the same kind")
+        hidden = self.weight.shape[0]
+        n_rows = stream.residual.shape[0] if rows is None else rows.shape[0]
+        out = torch.empty((n_rows, hidden), dtype=self.ctx.dtype, device=stream.residual.device)
+        ops.tanh_norm(stream.residual, stream.delta, after.triple if after is not None and stream.delta is not None else None,
+                      self.triple, out, rows=rows, write_residual=rows is None)
+        if rows is None:
+            stream.delta = stream.delta_norm = None
+        return out

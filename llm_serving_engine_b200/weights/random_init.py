@@ -6,7 +6,7 @@ tensors later.  Distributions: matrices and embeddings N(0, 0.02) (the
 reference's initialisation, ``src/llmserve/model.py:253-258``); biases
 N(0, 0.02) and norm weights 1 + U(-0.1, 0.1), not the reference's zeros and
 ones, so that a wrong bias or norm shows in the logits; mixing matrices identity +
-U(-0.1, 0.1); positive vectors U(0.1, 1).
+U(-0.1, 0.1); positive vectors U(0.1, 1); convolution weights N(0, 0.3).
 """
 from __future__ import annotations
 
@@ -33,6 +33,8 @@ def random_tensor(name: str, spec: TensorSpec, seed: int) -> torch.Tensor:
         return torch.randn(spec.shape, generator=generator, dtype=torch.float32) * 0.02
     if spec.kind == "norm":
         return 1.0 + (torch.rand(spec.shape, generator=generator, dtype=torch.float32) * 0.2 - 0.1)
+    if spec.kind == "filter":
+        return torch.randn(spec.shape, generator=generator, dtype=torch.float32) * 0.3
     if spec.kind == "positive":
         return 0.1 + 0.9 * torch.rand(spec.shape, generator=generator, dtype=torch.float32)
     if spec.kind == "mixing":

@@ -23,6 +23,7 @@ from pathlib import Path
 RANDOM_MODELS = {
     "givelix": dict(vocab_size=260),     # the Givelix design at a small size (``_givelix_stand_in``)
     "fororax": dict(vocab_size=260),     # the Fororax design at a small size (``_fororax_stand_in``)
+    "tufevik": dict(vocab_size=260),     # the Tufevik design at a small size (``_tufevik_stand_in``)
     # the reference's ModelConfig.tiny (src/llmserve/config.py:34-44) over the byte tokenizer's vocabulary
     "tiny": dict(vocab_size=260, hidden_size=128, intermediate_size=352, num_hidden_layers=4, num_attention_heads=4,
                  num_key_value_heads=2, max_position_embeddings=1024, rope_theta=10000.0, rms_norm_eps=1e-6),
@@ -60,8 +61,26 @@ def _fororax_stand_in(vocab_size: int) -> dict:
                        {"type": "attention", "mixer": dict(heads, kv_from=1), "mlp": mlp}]}
 
 
+def _tufevik_stand_in(vocab_size: int) -> dict:
+    """A small model of the Tufevik design: a matrix-memory layer with a dense feed-forward, a layer with attention and
+    a selective scan side by side over a mixture of experts, a matrix-memory layer over a mixture."""
+    mlp = {"kind": "moe", "router": {"experts": 6, "top": 2}, "expert": {"ff": 96}}
+    memory = {"heads": 4, "dim": 32, "vdim": 32, "gate_cap": 15.0}
+    left = {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "conv": 4, "scale": 32 ** -0.5,
+            "rot": {"base": 10000.0, "dims": 16, "scaling": {"factor": 4.0, "original": 256, "fast": 32.0, "slow": 1.0}}}
+    right = {"inner": 128, "state": 16, "dt_rank": 8, "conv": 4}
+    return {"architecture": "Tufevik", "vocab": vocab_size, "width": 128, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 128 ** 0.5}, "max_position_embeddings": 1024,
+            "layers": [{"type": "mlstm", "mixer": memory, "mlp": {"kind": "dense", "ff": 352}},
+                       {"type": "parallel", "mlp": mlp,
+                        "mixer": {"left": left, "right": right, "left_scale": 0.5, "right_scale": 0.5}},
+                       {"type": "mlstm", "mixer": memory, "mlp": mlp}]}
+
+
 def tiny_config(vocab_size: int = 260, name: str = "tiny") -> dict:
     """config.json of a random stand-in model."""
+    if name == "tufevik":
+        return _tufevik_stand_in(vocab_size)
     if name == "fororax":
         return _fororax_stand_in(vocab_size)
     if name == "givelix":

@@ -41,7 +41,7 @@ _ATTENTION_NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o", "q_no
 class ConvRotaryAttention(BranchMixer):
     """params: ``heads``, ``kv_heads`` (query head h uses key/value head h // (heads / kv_heads)), ``dim`` (of a head's
     query and key), ``vdim`` (of its value), ``conv`` (taps of the short causal convolution that q, k and v each
-    pass, per channel, straight after their projection; 1: none), ``eps`` (of the norms), ``rot`` ({base, dims,
+    pass, per channel, straight after their projection; 0 or absent: none, and no such tensors), ``eps`` (of the norms), ``rot`` ({base, dims,
     scaling}: the first ``dims`` values of every head are rotated, value i paired with i + dims / 2; see
     ``rotary_frequencies`` for ``scaling``), ``scale`` (on the scores), ``gate`` (head h's output times
     sigmoid(w_g,h x)), ``tensor_names``.
@@ -59,7 +59,7 @@ class ConvRotaryAttention(BranchMixer):
         super().__init__(params, weights, ctx)
         p = params
         self.n_q, self.n_kv = int(p["heads"]), int(p["kv_heads"])
-        self.dk, self.dv, self.taps = int(p["dim"]), int(p["vdim"]), int(p.get("conv", 1))
+        self.dk, self.dv, self.taps = int(p["dim"]), int(p["vdim"]), max(int(p.get("conv", 0)), 1)
         self.scale, self.eps = float(p["scale"]), float(p["eps"])
         if self.n_q % self.n_kv:
             raise ops.KernelError(f"attention: {self.n_q} query heads do not divide into {self.n_kv} groups")
@@ -75,7 +75,7 @@ class ConvRotaryAttention(BranchMixer):
         if self.has_gate:
             stacked.append(weights[names["gate"]])
         self.in_weight = torch.cat(stacked, dim=0).contiguous()
-        if self.taps > 1:
+        if int(p.get("conv", 0)) >= 1:
             self.conv_weight = torch.cat([weights[names[role] + names["conv_suffix"]].to(torch.float32)
                                           for role in ("q", "k", "v")], dim=0).contiguous()
         else:
@@ -87,12 +87,12 @@ class ConvRotaryAttention(BranchMixer):
     @classmethod
     def expected_tensors(cls, params, hidden_size):
         p = params
-        n_q, n_kv, dk, dv, taps = int(p["heads"]), int(p["kv_heads"]), int(p["dim"]), int(p["vdim"]), int(p.get("conv", 1))
+        n_q, n_kv, dk, dv, taps = int(p["heads"]), int(p["kv_heads"]), int(p["dim"]), int(p["vdim"]), int(p.get("conv", 0))
         names = {**_ATTENTION_NAMES, **p.get("tensor_names", {})}
         out = {names["q"]: TensorSpec((n_q * dk, hidden_size)), names["k"]: TensorSpec((n_kv * dk, hidden_size)),
                names["v"]: TensorSpec((n_kv * dv, hidden_size)), names["out"]: TensorSpec((hidden_size, n_q * dv)),
                names["q_norm"]: TensorSpec((n_q * dk,), "norm"), names["k_norm"]: TensorSpec((n_kv * dk,), "norm")}
-        if taps > 1:
+        if taps >= 1:
             for role in ("q", "k", "v"):
                 out[names[role] + names["conv_suffix"]] = TensorSpec((out[names[role]].shape[0], taps), "filter")
         if p.get("gate", False):
@@ -102,7 +102,7 @@ class ConvRotaryAttention(BranchMixer):
     @classmethod
     def cache_requirement(cls, params, hidden_size):
         n_q, n_kv, dk, dv = int(params["heads"]), int(params["kv_heads"]), int(params["dim"]), int(params["vdim"])
-        taps = int(params.get("conv", 1))
+        taps = int(params.get("conv", 0))
         pages = PagedKV(n_kv, dk, 0, 0 if dv == dk else dv)
         return (pages, RequestState((max(taps - 1, 0), (n_q + n_kv) * dk + n_kv * dv), "float32"))
 

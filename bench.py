@@ -562,7 +562,16 @@ FORORAX_SIZES = {
     "w2048": dict(width=2048, heads=16, ff=8192),
     "w4096": dict(width=4096, heads=32, ff=16384),
 }
-DESIGN_SIZES = {"givelix": GIVELIX_SIZES, "fororax": FORORAX_SIZES}
+# Tufevik at layer sizes that resemble real models of the kind: six layers, matrix-memory layers and layers with an
+# attention and a selective scan side by side in turn; heads of 128 (the attention's in groups of eight, half of a head
+# rotated, four taps), a scan of as many channels as the model is wide with sixteen states a channel and a step-size
+# rank of a sixteenth of the width; dense feed-forwards and mixtures of eight experts of half the dense size of which a
+# token uses two in turn, so that a token's feed-forward work equals the dense layer's.
+TUFEVIK_SIZES = {
+    "w2048": dict(width=2048, heads=16, ff=8192),
+    "w4096": dict(width=4096, heads=32, ff=16384),
+}
+DESIGN_SIZES = {"givelix": GIVELIX_SIZES, "fororax": FORORAX_SIZES, "tufevik": TUFEVIK_SIZES}
 
 
 def fororax_config(width: int, heads: int, ff: int, vocab: int = 32768, context: int = 4096) -> dict:
@@ -575,6 +584,21 @@ def fororax_config(width: int, heads: int, ff: int, vocab: int = 32768, context:
               for index, kind in enumerate(kinds)]
     return {"architecture": "Fororax", "vocab": vocab, "width": width, "max_positions": context, "layers": layers,
             "norm": {"eps": 1e-6}, "postln_alpha": 2.0, "embedding": {"scale": 1.0}, "logit_softcap": 30.0}
+
+
+def tufevik_config(width: int, heads: int, ff: int, vocab: int = 32768, context: int = 4096) -> dict:
+    dense = {"kind": "dense", "ff": ff}
+    mixture = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 2}}
+    memory = {"heads": heads, "dim": 128, "vdim": 128, "gate_cap": 15.0}
+    left = {"heads": heads, "kv_heads": max(2, heads // 8), "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5,
+            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+    right = {"inner": width, "state": 16, "dt_rank": width // 16, "conv": 4}
+    side_by_side = {"left": left, "right": right, "left_scale": 0.5, "right_scale": 0.5}
+    layers = [{"type": "mlstm", "mixer": memory, "mlp": dense}, {"type": "parallel", "mixer": side_by_side, "mlp": mixture},
+              {"type": "mlstm", "mixer": memory, "mlp": mixture}, {"type": "parallel", "mixer": side_by_side, "mlp": dense},
+              {"type": "mlstm", "mixer": memory, "mlp": dense}, {"type": "parallel", "mixer": side_by_side, "mlp": mixture}]
+    return {"architecture": "Tufevik", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "max_position_embeddings": context}
 
 
 def kernel_times(run, repeats: int = 3) -> dict:
@@ -625,8 +649,8 @@ def run_design(args) -> dict:
     peak = peaks()
     fma_tflops = 2 * 128 * torch.cuda.get_device_properties(0).multi_processor_count * 1.965e9 / 1e12   # float32 FMA pipe
     design = args.design
-    make_config = {"givelix": givelix_config, "fororax": fororax_config}[design]
-    rooflines = {"givelix": design_rooflines, "fororax": fororax_rooflines}[design]
+    make_config = {"givelix": givelix_config, "fororax": fororax_config, "tufevik": tufevik_config}[design]
+    rooflines = {"givelix": design_rooflines, "fororax": fororax_rooflines, "tufevik": tufevik_rooflines}[design]
     batch, out = args.batch, {"design": design, "peaks": dict(peak, fp32_fma_tflops=round(fma_tflops, 1)), "sizes": {}}
     names = [args.design_size] if args.design_size else list(DESIGN_SIZES[design])
     with ClockSampler() as clocks:
@@ -783,6 +807,80 @@ def fororax_rooflines(shape: dict, entry: dict, batch: int, peak: dict, fma_tflo
     out["decode"]["fororax scaled_add_rmsnorm"] = frac(f["decode_kernels"], "scaled_add_rmsnorm", 12, batch * width * (4 * 2 + 4 + 2), 0, fma)
     out["decode"]["fororax rows of the mixture (route, activation)"] = frac(
         f["decode_kernels"], ("moe_",), 6, (experts + 3) * width * 2 + batch * (experts * expert_ff + shared_ff) * 2 * 3, 0, fma)
+    out["decode"]["qwen2 add_rmsnorm"] = frac(q["decode_kernels"], "add_rmsnorm", 13, batch * width * (4 * 2 + 4 + 2), 0, fma)
+    return out
+
+
+def tufevik_rooflines(shape: dict, entry: dict, batch: int, peak: dict, fma_tflops: float) -> dict:
+    """As :func:`design_rooflines`, for Tufevik beside Qwen2.  The matrix memory's scan and the selective scan keep
+    float32 states by the design's own rule and are set against the float32 FMA pipe (an exponential counted as one
+    operation) or the bytes they move, whichever is slower; the attention against the measured bfloat16 tensor
+    throughput; the row-wise kernels (tanh norms, convolutions with norms and rotation, gates, read-outs) against the
+    bytes they move."""
+    heads, width, tokens = shape["heads"], shape["width"], PROMPT
+    kv_heads = max(2, heads // 8)
+    config = tufevik_config(**shape)
+    right = config["layers"][1]["mixer"]["right"]
+    inner, states, rank = right["inner"], right["state"], right["dt_rank"]
+    mixture = config["layers"][1]["mlp"]
+    experts, top, expert_ff = mixture["router"]["experts"], mixture["router"]["top"], mixture["expert"]["ff"]
+    bandwidth, tensor, fma = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12, fma_tflops * 1e12
+
+    def frac(kernels: dict, keys, launches_of_work: float, bytes_each: float, flops_each: float, pipe: float):
+        keys = (keys,) if isinstance(keys, str) else keys
+        found = [(name, value) for name, value in kernels.items() if any(key in name for key in keys)]
+        if not found:
+            return None
+        us = sum(value["us"] for _, value in found)
+        count = sum(value["launches"] for _, value in found)
+        bound = max(bytes_each / bandwidth, flops_each / pipe) * launches_of_work
+        return {"us": round(us, 1), "launches": count, "bound_us": round(bound * 1e6, 2), "frac": round(bound * 1e6 / us, 4)}
+
+    pairs = tokens * (tokens + 1) / 2
+    t, q = entry["tufevik"], entry["qwen2_equal_size"]
+    out = {"prefill": {}, "decode": {}}
+    channels = (heads + 2 * kv_heads) * 128
+    # prompt step: three matrix-memory layers, three layers with attention and scan side by side
+    out["prefill"]["tufevik matrix memory scan + carry (float32 FMA)"] = frac(
+        t["prefill_kernels"], "linear_attention", 3, tokens * heads * (128 * 3 * 4 + 129 * 4), tokens * heads * 128 * 129 * 2 * 4, fma)
+    out["prefill"]["tufevik matrix memory gates + read-out"] = frac(
+        t["prefill_kernels"], ("mlstm_gates", "mlstm_readout"), 3, tokens * heads * (129 * 4 + 128 * 4 + 128 * 2 + 5 * 4), 0, fma)
+    out["prefill"]["tufevik selective scan (float32 FMA)"] = frac(
+        t["prefill_kernels"], "selective_scan", 3, tokens * inner * (2 + 4 + 4 + 2) + tokens * 2 * states * 4,
+        tokens * inner * states * 6, fma)
+    out["prefill"]["tufevik step sizes + convolution of the scan's inputs"] = frac(
+        t["prefill_kernels"], ("ssm_step_sizes", "short_conv_act"), 3, tokens * inner * (4 + 2) + tokens * inner * 4,
+        2 * tokens * inner * rank, fma)
+    out["prefill"]["tufevik attention (3 layers)"] = frac(
+        t["prefill_kernels"], ("attention_scored", "attn_prefill_tc"), 3, tokens * channels * 2 * 2, 4 * pairs * heads * 128, tensor)
+    out["prefill"]["tufevik conv_qk_norm_rope (+ head gates)"] = frac(
+        t["prefill_kernels"], ("conv_qk_norm_rope", "head_gate_scale"), 3, tokens * channels * (4 + 2) + tokens * heads * 128 * 4, 0, fma)
+    out["prefill"]["tufevik tanh_norm"] = frac(t["prefill_kernels"], "tanh_norm", 13, tokens * width * (4 * 2 + 4 + 2), 0, fma)
+    out["prefill"]["tufevik rows of the mixture (route, place, gather, activation, combine)"] = frac(
+        t["prefill_kernels"], ("moe_",), 3, tokens * width * 2 * (1 + 2 * top) + tokens * top * expert_ff * 2 * 3 + tokens * width * 4 * 2, 0, fma)
+    out["prefill"]["qwen2 attention (tcgen05)"] = frac(
+        q["prefill_kernels"], "attn_", 6, tokens * channels * 2 * 2, 4 * pairs * heads * 128, tensor)
+    out["prefill"]["qwen2 add_rmsnorm"] = frac(q["prefill_kernels"], "add_rmsnorm", 13, tokens * width * (4 * 2 + 2 + 2), 0, fma)
+    out["prefill"]["qwen2 rope_kv_write"] = frac(q["prefill_kernels"], "rope_kv_write", 6, tokens * channels * 2 * 2, 0, fma)
+    # decode step at `batch` requests over 2,048-token contexts: the states are read and written once a token
+    kv_bytes = batch * tokens * 2 * kv_heads * 128 * 2
+    out["decode"]["tufevik matrix memory scan"] = frac(
+        t["decode_kernels"], "linear_attention", 3, batch * heads * 128 * 129 * 4 * 2, batch * heads * 128 * 129 * 4, fma)
+    out["decode"]["tufevik matrix memory gates + read-out"] = frac(
+        t["decode_kernels"], ("mlstm_gates", "mlstm_readout"), 3, batch * heads * (129 * 4 + 128 * 4 + 128 * 2), 0, fma)
+    out["decode"]["tufevik selective scan"] = frac(
+        t["decode_kernels"], "selective_scan", 3, batch * inner * states * 4 * 2 + inner * states * 4, batch * inner * states * 6, fma)
+    out["decode"]["tufevik step sizes + convolution of the scan's inputs"] = frac(
+        t["decode_kernels"], ("ssm_step_sizes", "short_conv_act"), 3, inner * rank * 4 + batch * inner * 4 * 4, 2 * batch * inner * rank, fma)
+    out["decode"]["tufevik attention (chunks + merge)"] = frac(
+        t["decode_kernels"], ("attention_scored",), 3, kv_bytes, 4 * batch * tokens * heads * 128, tensor)
+    out["decode"]["tufevik conv_qk_norm_rope (+ head gates)"] = frac(
+        t["decode_kernels"], ("conv_qk_norm_rope", "head_gate_scale"), 3, batch * channels * 4 * 5, 0, fma)
+    out["decode"]["tufevik tanh_norm"] = frac(t["decode_kernels"], "tanh_norm", 13, batch * width * (4 * 2 + 4 + 2), 0, fma)
+    out["decode"]["tufevik rows of the mixture (route, activation)"] = frac(
+        t["decode_kernels"], ("moe_",), 3, (experts + 1) * width * 2 + batch * experts * expert_ff * 2 * 3, 0, fma)
+    out["decode"]["qwen2 attention (mma.sync, split keys)"] = frac(
+        q["decode_kernels"], "attn_", 6, kv_bytes, 4 * batch * tokens * heads * 128, tensor)
     out["decode"]["qwen2 add_rmsnorm"] = frac(q["decode_kernels"], "add_rmsnorm", 13, batch * width * (4 * 2 + 4 + 2), 0, fma)
     return out
 
@@ -1107,7 +1205,7 @@ def main() -> int:
                         help="with --only: the true float32 path instead of the serving precision")
     parser.add_argument("--quick", action="store_true", help="the headline, its points and the end-to-end number only "
                                                              "(no other model sizes, no float32 point, no kernel table)")
-    parser.add_argument("--design", choices=("givelix", "fororax"), default=None,
+    parser.add_argument("--design", choices=("givelix", "fororax", "tufevik"), default=None,
                         help="instead of the default workload: the named design at layer sizes of real models beside the "
                              "Qwen2 model of equal size (prefill and decode throughput, kernel times, rooflines)")
     parser.add_argument("--design-size", choices=tuple(sorted({name for sizes in DESIGN_SIZES.values() for name in sizes})),

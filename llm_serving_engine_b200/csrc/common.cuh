@@ -27,6 +27,22 @@ template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
 template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 
+// The value of an element that arrives as n_partials partial sums partial_stride elements apart (one: the element
+// itself): added in index order, starting from zero, as every consumer of such a stack adds them.  Four loads are in
+// flight at a time, so that a stack of sixteen costs four round trips, not sixteen.
+template <typename T>
+__device__ __forceinline__ float sum_partials(const T* p, int n_partials, long long partial_stride) {
+  float v = 0.f;
+  int i = 0;
+  for (; i + 4 <= n_partials; i += 4) {
+    const float a = to_f32<T>(p[(size_t)i * partial_stride]), b = to_f32<T>(p[(size_t)(i + 1) * partial_stride]);
+    const float c = to_f32<T>(p[(size_t)(i + 2) * partial_stride]), d = to_f32<T>(p[(size_t)(i + 3) * partial_stride]);
+    v += a; v += b; v += c; v += d;
+  }
+  for (; i < n_partials; ++i) v += to_f32<T>(p[(size_t)i * partial_stride]);
+  return v;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
   for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

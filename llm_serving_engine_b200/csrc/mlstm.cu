@@ -17,9 +17,7 @@ LSE_CHECK_DEFINE(lse_check_mlstm)
 namespace {
 template <typename TD>
 __device__ __forceinline__ float ml_load(const TD* p, int n_partials, long long partial_stride) {
-  float v = 0.f;
-  for (int i = 0; i < n_partials; ++i) v += to_f32<TD>(p[(size_t)i * partial_stride]);
-  return v;
+  return sum_partials<TD>(p, n_partials, partial_stride);
 }
 
 __device__ __forceinline__ float ml_logsigmoid(float z) {
@@ -70,19 +68,21 @@ mlstm_gates_kernel(const TD* __restrict__ proj, int n_partials, long long partia
   if (lane == 0) *m_at = m;
 }
 
-// read [T, heads, vdim + 1]: the scan's outputs, the last column n . q.  A warp per (token, head) at a time.
+// read [T, heads, vdim + 1]: the scan's outputs, the last column n . q.  A warp per (token, head).
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(128)
 mlstm_readout_kernel(const float* __restrict__ read, const float* __restrict__ floor_in, const TD* __restrict__ proj,
                      int n_partials, long long partial_stride, long long ld, int g_off,
-                     const float* __restrict__ weight, TO* __restrict__ out, int heads, int vdim, float eps,
+                     const float* __restrict__ weight, TO* __restrict__ out, int tokens, int heads, int vdim, float eps,
                      const int* __restrict__ segment_of_token) {
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x;
-  if (segment_of_token && segment_of_token[t] < 0) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  for (int h = warp; h < heads; h += warps) {
+  const long long pair = (long long)blockIdx.x * warps + warp;      // (token, head): a warp each, so that few rows fill the GPU too
+  if (pair >= (long long)tokens * heads) return;
+  const int t = (int)(pair / heads), h = (int)(pair % heads);
+  if (segment_of_token && segment_of_token[t] < 0) return;
+  {
     const float* row = read + ((size_t)t * heads + h) * (vdim + 1);
     const float inv_den = 1.0f / (fmaxf(fabsf(row[vdim]), floor_in[(size_t)t * heads + h]) + 1e-6f);
     float sq = 0.f;
@@ -131,8 +131,9 @@ extern "C" int lse_mlstm_readout(const float* read, const float* floor_in, const
   if (tokens <= 0) return 0;
   if (heads <= 0 || vdim <= 0 || n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
 #define LSE_ML_CASE(TD, TO)                                                                                          \
-  lse_launch(mlstm_readout_kernel<TD, TO>, tokens, 128, 0, stream, read, floor_in, (const TD*)proj, n_partials,      \
-             partial_stride, ld, g_off, weight, (TO*)out, heads, vdim, eps, segment_of_token)
+  lse_launch(mlstm_readout_kernel<TD, TO>, (unsigned)(((long long)tokens * heads + 3) / 4), 128, 0, stream, read,    \
+             floor_in, (const TD*)proj, n_partials, partial_stride, ld, g_off, weight, (TO*)out, tokens, heads, vdim, \
+             eps, segment_of_token)
   const bool d32 = proj_dtype == LSE_DTYPE_F32, o32 = out_dtype == LSE_DTYPE_F32;
   if (d32 && o32) LSE_ML_CASE(float, float);
   else if (d32 && !o32) LSE_ML_CASE(float, __nv_bfloat16);

@@ -20,9 +20,7 @@ LSE_CHECK_DEFINE(lse_check_short_conv)
 namespace {
 template <typename TD>
 __device__ __forceinline__ float sc_load(const TD* p, int n_partials, long long partial_stride) {
-  float v = 0.f;
-  for (int i = 0; i < n_partials; ++i) v += to_f32<TD>(p[(size_t)i * partial_stride]);
-  return v;
+  return sum_partials<TD>(p, n_partials, partial_stride);
 }
 
 // The convolution's sum for row `r` (local index l = r - row0 in its request's rows of this step) and channel c.
@@ -31,12 +29,21 @@ __device__ __forceinline__ float sc_conv(const TD* __restrict__ proj, int n_part
                                          long long ld, int off, const float* __restrict__ weight,
                                          const float* __restrict__ window, int channels, int taps, int r, int l, int c) {
   float y = 0.f;
-  for (int j = 0; j < taps; ++j) {
-    const int back = taps - 1 - j;         // how many tokens before row r
-    float u;
-    if (l - back >= 0) u = sc_load(proj + (size_t)(r - back) * ld + off + c, n_partials, partial_stride);
-    else u = window[(size_t)(taps - 1 + l - back) * channels + c];
-    y = fmaf(weight[(size_t)c * taps + j], u, y);
+  for (int j0 = 0; j0 < taps; j0 += 4) {     // four taps' inputs and weights are fetched before any is used
+    float u[4], w[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int j = j0 + i, back = taps - 1 - j;         // back: how many tokens before row r
+      u[i] = w[i] = 0.f;
+      if (j < taps) {
+        w[i] = weight[(size_t)c * taps + j];
+        if (l - back >= 0) u[i] = sc_load(proj + (size_t)(r - back) * ld + off + c, n_partials, partial_stride);
+        else u[i] = window[(size_t)(taps - 1 + l - back) * channels + c];
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      if (j0 + i < taps) y = fmaf(w[i], u[i], y);
   }
   return y;
 }

@@ -131,7 +131,8 @@ _SIGNATURES = {
                            c_int, c_void_p],
     "lse_selective_scan": [c_void_p, c_int, c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p,
                            c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
-                           c_void_p, c_void_p, c_int, c_longlong, c_float, c_int, c_int, c_int, c_int, c_void_p],
+                           c_void_p, c_void_p, c_int, c_longlong, c_float, c_int, c_int, c_int, c_int, c_int, c_void_p,
+                           c_void_p, c_int, c_void_p],
     "lse_moe_route_biased": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                              c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "lse_moe_gated_act_kind": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,

@@ -1212,6 +1212,10 @@ def head_gate_scale(attended: torch.Tensor, gate: torch.Tensor | None, out: torc
 
 
 # ------------------------------------------------------------------ selective state-space scan
+SELECTIVE_SCAN_CHUNK = 64          # rows of a chunk when a step's rows are scanned in chunks
+SELECTIVE_SCAN_CHUNKED_FROM = 128  # rows of a step from which they are
+
+
 def ssm_step_sizes(low: torch.Tensor, weight_t: torch.Tensor, bias: torch.Tensor) -> torch.Tensor:
     """dt float32 [T, C] = softplus(low[:, :rank] @ weight_t + bias); ``low``: a projection's rows (or partial sums),
     ``weight_t`` float32 [rank, C]."""
@@ -1230,12 +1234,14 @@ def ssm_step_sizes(low: torch.Tensor, weight_t: torch.Tensor, bias: torch.Tensor
 
 def selective_scan(x: torch.Tensor, dt: torch.Tensor, proj: torch.Tensor, z_off: int, low: torch.Tensor, b_off: int,
                    c_off: int, a_log: torch.Tensor, skip: torch.Tensor, state: torch.Tensor, step, out: torch.Tensor,
-                   scale: float = 1.0) -> torch.Tensor:
+                   scale: float = 1.0, chunked: bool | None = None) -> torch.Tensor:
     """S[c, n] <- exp(dt[c] A[c, n]) S[c, n] + dt[c] x[c] B[n];  y[c] = sum_n S[c, n] C[n] + skip[c] x[c];
     out[t, c] = y[c] silu(z[c]) * scale, over the rows of every request in order, from and into ``state`` float32
     [slots, C, N].  A = -exp(a_log) (float32 [C, N]); B and C are columns b_off .. and c_off .. of ``low``, z columns
     z_off .. of ``proj`` (each a projection's rows or partial sums); x [T, C] in the compute dtype, dt float32 [T, C];
-    ``out`` [T, C] may be a column range of a wider tensor."""
+    ``out`` [T, C] may be a column range of a wider tensor.  ``chunked`` (default: from ``SELECTIVE_SCAN_CHUNKED_FROM``
+    rows on): the rows of a request are cut into chunks that are scanned side by side, each from zero, then carried
+    (a chunk's decay is exp(A * the sum of its step sizes)), then scanned again for the outputs."""
     _need_cuda(x, dt, proj, low, a_log, skip, state, out)
     proj, p_code, p_partials, p_stride, p_ld = _projection(proj)
     low, l_code, l_partials, l_stride, l_ld = _projection(low)
@@ -1246,10 +1252,16 @@ def selective_scan(x: torch.Tensor, dt: torch.Tensor, proj: torch.Tensor, z_off:
     assert skip.shape == (channels,)
     assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (channels, states)
     assert out.shape == (tokens, channels) and out.stride(1) == 1 and out.dtype == x.dtype
+    chunk_rows, chunk_state, chunk_dt, max_chunks = 0, None, None, 0
+    if chunked if chunked is not None else tokens >= SELECTIVE_SCAN_CHUNKED_FROM:
+        chunk_rows = SELECTIVE_SCAN_CHUNK
+        max_chunks = tokens // chunk_rows + step.segment_state_slot.shape[0]
+        chunk_state = torch.empty((max_chunks, channels, states), dtype=torch.float32, device=out.device)
+        chunk_dt = torch.empty((max_chunks, channels), dtype=torch.float32, device=out.device)
     check(library.load().lse_selective_scan(
         x.data_ptr(), dtype_code(x.dtype), dt.data_ptr(), proj.data_ptr(), p_code, p_partials, p_stride, p_ld, int(z_off),
         low.data_ptr(), l_code, l_partials, l_stride, l_ld, int(b_off), int(c_off), a_log.data_ptr(), skip.data_ptr(),
         state.data_ptr(), step.segment_start.data_ptr(), step.segment_state_slot.data_ptr(), out.data_ptr(),
         dtype_code(out.dtype), out.stride(0), float(scale), step.segment_state_slot.shape[0], channels, states,
-        state.shape[0], _stream()), "selective_scan")
+        state.shape[0], chunk_rows, _ptr(chunk_state), _ptr(chunk_dt), max_chunks, _stream()), "selective_scan")
     return out

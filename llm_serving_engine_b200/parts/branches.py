@@ -10,6 +10,7 @@ from .base import MIXERS, Mixer, PagedKV, RequestState, cache_for, cache_needs, 
 from .latent_attention import rotary_frequencies
 from .linear import linear_partials
 from .mlstm import input_projection
+from .normed_attention import prompt_shape_for_tcgen05
 
 
 class BranchMixer(Mixer):
@@ -51,7 +52,8 @@ class ConvRotaryAttention(BranchMixer):
     ``conv - 1`` projected rows [q | k | v] (float32), so that a step may start anywhere.
 
     One kernel does convolution, norms, rotation, the page write and the gates' sigmoid; the attention itself is the
-    engine's paged attention for keys and values of any sizes (tensor cores for bfloat16 shapes that it takes)."""
+    engine's paged attention for keys and values of any sizes (tensor cores for bfloat16 shapes that it takes; long
+    prompt portions with heads of 64 or 128 on the tcgen05 kernel)."""
 
     graph_safe = True
 
@@ -106,6 +108,14 @@ class ConvRotaryAttention(BranchMixer):
         pages = PagedKV(n_kv, dk, 0, 0 if dv == dk else dv)
         return (pages, RequestState((max(taps - 1, 0), (n_q + n_kv) * dk + n_kv * dv), "float32"))
 
+    def _on_tcgen05(self, segment_counts, page_size=None) -> bool:
+        if not prompt_shape_for_tcgen05(self.ctx.dtype, self.dk, self.dv, segment_counts):
+            return False
+        return page_size is None or ops.attention_tc_supported(self.dk, self.n_q, self.n_kv, page_size, self.ctx.dtype)
+
+    def launch_signature(self, segment_counts):
+        return ("tcgen05",) if self._on_tcgen05(segment_counts) else ()
+
     def inner(self, proj, offset, step, cache, out, scale):
         pages, window = cache.parts[0], cache.parts[1].state
         tokens = out.shape[0]
@@ -117,9 +127,14 @@ class ConvRotaryAttention(BranchMixer):
         if self.taps > 1:
             ops.short_conv_state(proj, offset, self.channels, self.taps, window, step)
         attended = torch.empty((tokens, self.n_q, self.dv), dtype=out.dtype, device=out.device)
-        ops.attention_scored(q, pages.keys, pages.values, attended, pages.block_tables, step.segment_of_token,
-                             step.positions, self.scale, segment_start=step.segment_start,
-                             segment_first_position=step.segment_first_position)
+        if (not step.decode_only and step.segments
+                and self._on_tcgen05([segment.count for segment in step.segments], pages.keys.shape[2])):
+            ops.attention_scored_tc(q, pages.keys, pages.values, attended, pages.block_tables, step.segment_start,
+                                    step.segment_first_position, self.scale)
+        else:
+            ops.attention_scored(q, pages.keys, pages.values, attended, pages.block_tables, step.segment_of_token,
+                                 step.positions, self.scale, segment_start=step.segment_start,
+                                 segment_first_position=step.segment_first_position)
         ops.head_gate_scale(attended, gate, out, scale, step.segment_of_token)
 
 

@@ -16,6 +16,16 @@ TCGEN05_MIN_ROWS = 128
 TCGEN05_MIN_ROWS_PER_REQUEST = 64
 TCGEN05 = os.environ.get("LSE_SCORED_TCGEN05", "1") != "0"
 
+
+def prompt_shape_for_tcgen05(dtype, dk: int, dv: int, segment_counts: list[int]) -> bool:
+    """Whether a step of these portions, with heads of these sizes, is one for ``ops.attention_scored_tc``: bfloat16, keys
+    and values of one size that is 64 or 128, a portion of at least 128 rows, portions long on average (a single token
+    would take a tile of 128 rows)."""
+    if not TCGEN05 or dtype != torch.bfloat16 or dk != dv or dk not in (64, 128) or not segment_counts:
+        return False
+    return (max(segment_counts) >= TCGEN05_MIN_ROWS
+            and sum(segment_counts) >= TCGEN05_MIN_ROWS_PER_REQUEST * len(segment_counts))
+
 _DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "out": "o", "q_norm": "q.norm", "k_norm": "k.norm", "r1": "r1", "r2": "r2",
                   "sink": "sink", "mix": "talk", "gate": "g", "bias_suffix": ".b"}
 
@@ -114,9 +124,7 @@ class NormedAttention(Mixer):
     def _on_tcgen05(self, segment_counts: list[int], page_size: int | None = None) -> bool:
         """Whether a step of this shape takes the tcgen05 kernel: bfloat16, heads of 64 or 128 (keys and values alike), a
         portion of at least 128 rows, portions long on average (a single token would take a tile of 128 rows)."""
-        if not TCGEN05 or self.ctx.dtype != torch.bfloat16 or self.dk != self.dv or self.dk not in (64, 128):
-            return False
-        if max(segment_counts) < TCGEN05_MIN_ROWS or sum(segment_counts) < TCGEN05_MIN_ROWS_PER_REQUEST * len(segment_counts):
+        if not prompt_shape_for_tcgen05(self.ctx.dtype, self.dk, self.dv, segment_counts):
             return False
         if self.mix is not None and self.n_kv > 1 and not ops.head_mix_gate_stages(self.n_q, self.n_kv, self.dv):
             return False

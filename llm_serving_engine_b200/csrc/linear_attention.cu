@@ -21,7 +21,9 @@ constexpr int LA_DPT = 32;       // rows of the state that a thread keeps
 
 template <typename TD>
 __device__ __forceinline__ float la_load(const TD* p, int n_partials, long long partial_stride) {
-  return sum_partials<TD>(p, n_partials, partial_stride);
+  float v = 0.f;
+  for (int i = 0; i < n_partials; ++i) v += to_f32<TD>(p[(size_t)i * partial_stride]);
+  return v;
 }
 __device__ __forceinline__ float la_act(float z, int act) { return act == 1 ? z / (1.f + expf(-z)) : z; }
 

@@ -6,7 +6,7 @@
 // The gates kernel turns the gates' pre-activations (two columns per head of the layer's stacked projection) into the
 // three numbers per token and head that the scan and the read-out need,
 //     keep = exp(f_t + m_(t-1) - m_t),   take = exp(i_t - m_t),   floor = exp(-m_t),
-// walking each request's rows in order from the m that earlier steps left in the request's slot (zero for a new
+// following each request's rows in order from the m that earlier steps left in the request's slot (zero for a new
 // request) and leaving the new m there.  The scan itself is the gated form of the linear-attention scan
 // (linear_attention.cu), whose extra state column carries n.  The read-out kernel divides, norms every head by its
 // root mean square, and applies the norm weight and the output gate.  Everything is float32.
@@ -25,47 +25,65 @@ __device__ __forceinline__ float ml_logsigmoid(float z) {
   return fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
 }
 
-// One warp per (request, head).  The lanes work out the gates of 32 tokens at a time (the tanh, the exponential and
-// the logarithm are what costs); the recurrence of m then runs through those 32 tokens in order, every lane following
-// it, so that m is the same number whether the rows come in one step or in many.
+// One block of eight warps per (request, head), 256 tokens at a time.  The recurrence of m is a chain of maps
+// m -> max(m + f, i); two of them in a row are a map of the same form, (f1, i1) then (f2, i2) = (f1 + f2, max(i1 + f2, i2)),
+// so a warp scans its 32 tokens' maps with shuffles, the warps' totals are chained through shared memory, and every token
+// gets the m before it and its own.  keep uses exactly the m that the token before it was given, so the state's scale
+// stays consistent however the rows are cut into steps; m itself may differ from one cut to another in its last bits,
+// which moves nothing: it only says by what power the memory is scaled.
+constexpr int MG_THREADS = 256;
+
 template <typename TD>
-__global__ void __launch_bounds__(32)
+__global__ void __launch_bounds__(MG_THREADS)
 mlstm_gates_kernel(const TD* __restrict__ proj, int n_partials, long long partial_stride, long long ld, int i_off,
                    int f_off, const float* __restrict__ i_bias, const float* __restrict__ f_bias, float cap,
                    float* __restrict__ state_m, const int* __restrict__ segment_start,
                    const int* __restrict__ segment_slot, float* __restrict__ keep, float* __restrict__ take,
                    float* __restrict__ floor_out, int heads, int num_slots) {
+  __shared__ float total_f[MG_THREADS / 32], total_i[MG_THREADS / 32];
   pdl_launch_dependents();
   pdl_wait();
-  const int seg = blockIdx.x, h = blockIdx.y, lane = threadIdx.x;
+  const int seg = blockIdx.x, h = blockIdx.y, lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int row0 = segment_start[seg], row1 = segment_start[seg + 1];
   if (row1 <= row0) return;
   float* m_at = state_m + (size_t)LSE_CHECKED(segment_slot[seg], 0, num_slots, 0, LSE_CHECK_ROW) * heads + h;
   float m = *m_at;
   const float bi = i_bias[h], bf = f_bias[h];
-  for (int base = row0; base < row1; base += 32) {
-    const int n = min(32, row1 - base);
-    float gi = 0.f, gf = 0.f;
-    if (lane < n) {
-      const TD* row = proj + (size_t)(base + lane) * ld;
+  for (int base = row0; base < row1; base += MG_THREADS) {
+    const int r = base + threadIdx.x;
+    float gi = -INFINITY, gf = 0.f;      // past the last row: the map that changes nothing
+    if (r < row1) {
+      const TD* row = proj + (size_t)r * ld;
       gi = cap * tanhf((ml_load(row + i_off + h, n_partials, partial_stride) + bi) / cap);
       gf = ml_logsigmoid(cap * tanhf((ml_load(row + f_off + h, n_partials, partial_stride) + bf) / cap));
     }
-    float m_before = m, m_mine = m;
-    for (int j = 0; j < n; ++j) {
-      const float fj = __shfl_sync(0xffffffffu, gf, j), ij = __shfl_sync(0xffffffffu, gi, j);
-      const float next = fmaxf(fj + m, ij);
-      if (lane == j) { m_before = m; m_mine = next; }
-      m = next;
+    float sf = gf, si = gi;              // the maps of this warp's tokens up to and with this one, in one
+#pragma unroll
+    for (int o = 1; o < 32; o <<= 1) {
+      const float uf = __shfl_up_sync(0xffffffffu, sf, o), ui = __shfl_up_sync(0xffffffffu, si, o);
+      if (lane >= o) { si = fmaxf(ui + sf, si); sf = uf + sf; }
     }
-    if (lane < n) {
-      const size_t at = (size_t)(base + lane) * heads + h;
+    __syncthreads();                     // the totals of the round before have been read
+    if (lane == 31) { total_f[warp] = sf; total_i[warp] = si; }
+    __syncthreads();
+    float m_warp = m, m_next = m;        // m before this warp's first token; m after the block's last
+#pragma unroll
+    for (int w = 0; w < MG_THREADS / 32; ++w) {
+      m_next = fmaxf(m_next + total_f[w], total_i[w]);
+      if (w + 1 == warp) m_warp = m_next;
+    }
+    const float m_mine = fmaxf(m_warp + sf, si);
+    float m_before = __shfl_up_sync(0xffffffffu, m_mine, 1);
+    if (lane == 0) m_before = m_warp;
+    if (r < row1) {
+      const size_t at = (size_t)r * heads + h;
       keep[at] = expf(gf + m_before - m_mine);
       take[at] = expf(gi - m_mine);
       floor_out[at] = expf(-m_mine);
     }
+    m = m_next;
   }
-  if (lane == 0) *m_at = m;
+  if (threadIdx.x == 0) *m_at = m;
 }
 
 // read [T, heads, vdim + 1]: the scan's outputs, the last column n . q.  A warp per (token, head).
@@ -110,11 +128,11 @@ extern "C" int lse_mlstm_gates(const void* proj, int proj_dtype, int n_partials,
   if (heads <= 0 || heads > 65535 || !(cap > 0.f) || n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
   const dim3 grid(max_segments, heads);
   if (proj_dtype == LSE_DTYPE_F32)
-    lse_launch(mlstm_gates_kernel<float>, grid, 32, 0, stream, (const float*)proj, n_partials, partial_stride, ld,
+    lse_launch(mlstm_gates_kernel<float>, grid, MG_THREADS, 0, stream, (const float*)proj, n_partials, partial_stride, ld,
                i_off, f_off, i_bias, f_bias, cap, state_m, segment_start, segment_slot, keep, take, floor_out, heads,
                num_slots);
   else if (proj_dtype == LSE_DTYPE_BF16)
-    lse_launch(mlstm_gates_kernel<__nv_bfloat16>, grid, 32, 0, stream, (const __nv_bfloat16*)proj, n_partials,
+    lse_launch(mlstm_gates_kernel<__nv_bfloat16>, grid, MG_THREADS, 0, stream, (const __nv_bfloat16*)proj, n_partials,
                partial_stride, ld, i_off, f_off, i_bias, f_bias, cap, state_m, segment_start, segment_slot, keep, take,
                floor_out, heads, num_slots);
   else

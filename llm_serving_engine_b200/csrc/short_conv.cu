@@ -53,21 +53,23 @@ __global__ void __launch_bounds__(256)
 short_conv_act_kernel(const TD* __restrict__ proj, int n_partials, long long partial_stride, long long ld, int off,
                       const float* __restrict__ weight, const float* __restrict__ bias, const float* __restrict__ state,
                       const int* __restrict__ segment_of_token, const int* __restrict__ segment_start,
-                      const int* __restrict__ segment_slot, TO* __restrict__ out, int channels, int taps, int act,
-                      int num_slots, int num_segments) {
+                      const int* __restrict__ segment_slot, TO* __restrict__ out, int tokens, int rows_per_block,
+                      int channels, int taps, int act, int num_slots, int num_segments) {
   pdl_launch_dependents();
   pdl_wait();
-  const int r = blockIdx.x;
-  const int seg = segment_of_token[r];
-  if (seg < 0) return;
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= channels) return;
-  const int s = LSE_CHECKED(seg, 0, num_segments, 0, LSE_CHECK_SEGMENT);
-  const float* window = state + (size_t)LSE_CHECKED(segment_slot[s], 0, num_slots, 0, LSE_CHECK_ROW) * (taps - 1) * channels;
-  float y = sc_conv<TD>(proj, n_partials, partial_stride, ld, off, weight, window, channels, taps, r, r - segment_start[s], c);
-  if (bias) y += bias[c];
-  if (act == 1) y = y / (1.f + expf(-y));
-  out[(size_t)r * channels + c] = from_f32<TO>(y);
+  const float b = bias ? bias[c] : 0.f;
+  // a block takes rows_per_block rows one after the other: their inputs overlap, so all but one come from the cache
+  for (int r = blockIdx.x * rows_per_block, end = min(tokens, r + rows_per_block); r < end; ++r) {
+    const int seg = segment_of_token[r];
+    if (seg < 0) continue;
+    const int s = LSE_CHECKED(seg, 0, num_segments, 0, LSE_CHECK_SEGMENT);
+    const float* window = state + (size_t)LSE_CHECKED(segment_slot[s], 0, num_slots, 0, LSE_CHECK_ROW) * (taps - 1) * channels;
+    float y = sc_conv<TD>(proj, n_partials, partial_stride, ld, off, weight, window, channels, taps, r, r - segment_start[s], c) + b;
+    if (act == 1) y = y / (1.f + expf(-y));
+    out[(size_t)r * channels + c] = from_f32<TO>(y);
+  }
 }
 
 // The window after the step: entry i holds the input at position (first + count) - (taps - 1) + i.  In ascending i an
@@ -92,10 +94,10 @@ short_conv_state_kernel(const TD* __restrict__ proj, int n_partials, long long p
   }
 }
 
-// One block per row.  Channels: q (n_q * dk), then k (n_kv * dk), then v (n_kv * dv), consecutive columns from `off`,
+// One block per row (256 to 1024 threads).  Channels: q (n_q * dk), then k (n_kv * dk), then v (n_kv * dv), consecutive columns from `off`,
 // with their convolution weights stacked the same way; the gate's n_q columns start at g_off.
 template <typename TD, typename TO>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 conv_qk_norm_rope_kernel(const TD* __restrict__ proj, int n_partials, long long partial_stride, long long ld, int off,
                          int g_off, const float* __restrict__ weight, const float* __restrict__ state,
                          const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
@@ -195,11 +197,12 @@ extern "C" int lse_short_conv_act(const void* proj, int proj_dtype, int n_partia
                                   int num_segments, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (channels <= 0 || taps < 1 || n_partials < 1 || (channels + 255) / 256 > 65535) return LSE_ERR_BAD_ARGUMENT;
-  const dim3 grid(tokens, (channels + 255) / 256);
+  const int rows_per_block = tokens >= 1024 ? 8 : 1;
+  const dim3 grid((tokens + rows_per_block - 1) / rows_per_block, (channels + 255) / 256);
 #define LSE_SC_CASE(TD, TO)                                                                                         \
   lse_launch(short_conv_act_kernel<TD, TO>, grid, 256, 0, stream, (const TD*)proj, n_partials, partial_stride, ld, off, \
-             weight, bias, state, segment_of_token, segment_start, segment_slot, (TO*)out, channels, taps, act,      \
-             num_slots, num_segments)
+             weight, bias, state, segment_of_token, segment_start, segment_slot, (TO*)out, tokens, rows_per_block,   \
+             channels, taps, act, num_slots, num_segments)
   LSE_SC_TYPES(LSE_SC_CASE)
 #undef LSE_SC_CASE
   LSE_LAUNCH_CHECK();
@@ -241,11 +244,15 @@ extern "C" int lse_conv_qk_norm_rope(const void* proj, int proj_dtype, int n_par
     return LSE_ERR_BAD_ARGUMENT;
   const size_t smem = sizeof(float) * ((size_t)(n_q + n_kv) * dk + (size_t)n_kv * dv + rot_dims);
   if (smem > 200 * 1024) return LSE_ERR_TOO_LARGE;
+  // a thread's channels come one after the other, each a few dependent round trips: few rows get as many threads a row
+  // as a block has, many rows share the SMs
+  const int width = (n_q + n_kv) * dk + n_kv * dv;
+  const int threads = tokens <= 64 ? min(1024, (width + 31) / 32 * 32) : min(512, (width + 31) / 32 * 32);
 #define LSE_SC_CASE(TD, TO)                                                                                          \
   do {                                                                                                               \
     if (smem > 48 * 1024)                                                                                            \
       cudaFuncSetAttribute(conv_qk_norm_rope_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    lse_launch(conv_qk_norm_rope_kernel<TD, TO>, tokens, 256, smem, stream, (const TD*)proj, n_partials,             \
+    lse_launch(conv_qk_norm_rope_kernel<TD, TO>, tokens, threads, smem, stream, (const TD*)proj, n_partials,         \
                partial_stride, ld, off, g_off, weight, state, q_norm, k_norm, eps, freq, rot_factor, rot_dims,       \
                positions, segment_of_token, segment_start, segment_slot, slot_mapping, (TO*)q_out, (TO*)k_cache,     \
                (TO*)v_cache, gate_out, n_q, n_kv, dk, dv, taps, page_size, num_pages, num_slots, num_segments);      \

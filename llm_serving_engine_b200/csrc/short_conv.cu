@@ -24,10 +24,13 @@ __device__ __forceinline__ float sc_load(const TD* p, int n_partials, long long 
 }
 
 // The convolution's sum for row `r` (local index l = r - row0 in its request's rows of this step) and channel c.
-template <typename TD>
+// TAPS: the number of taps when the kernel was built for it (2, 3 or 4: the loops unroll), 0: any number, `taps`.
+// The sum runs over the taps in ascending order from zero in every form, so all forms give the same bits.
+template <typename TD, int TAPS>
 __device__ __forceinline__ float sc_conv(const TD* __restrict__ proj, int n_partials, long long partial_stride,
                                          long long ld, int off, const float* __restrict__ weight,
-                                         const float* __restrict__ window, int channels, int taps, int r, int l, int c) {
+                                         const float* __restrict__ window, int channels, int taps_rt, int r, int l, int c) {
+  const int taps = TAPS ? TAPS : taps_rt;
   float y = 0.f;
   for (int j0 = 0; j0 < taps; j0 += 4) {     // four taps' inputs and weights are fetched before any is used
     float u[4], w[4];
@@ -48,7 +51,9 @@ __device__ __forceinline__ float sc_conv(const TD* __restrict__ proj, int n_part
   return y;
 }
 
-template <typename TD, typename TO>
+// grid (tiles of rows_per_block rows, tiles of 256 channels).  With TAPS known a thread walks its rows with the last
+// TAPS - 1 inputs in registers (one new input a row; they are fetched afresh where a request begins inside the tile).
+template <typename TD, typename TO, int TAPS>
 __global__ void __launch_bounds__(256)
 short_conv_act_kernel(const TD* __restrict__ proj, int n_partials, long long partial_stride, long long ld, int off,
                       const float* __restrict__ weight, const float* __restrict__ bias, const float* __restrict__ state,
@@ -60,15 +65,48 @@ short_conv_act_kernel(const TD* __restrict__ proj, int n_partials, long long par
   const int c = blockIdx.y * blockDim.x + threadIdx.x;
   if (c >= channels) return;
   const float b = bias ? bias[c] : 0.f;
-  // a block takes rows_per_block rows one after the other: their inputs overlap, so all but one come from the cache
-  for (int r = blockIdx.x * rows_per_block, end = min(tokens, r + rows_per_block); r < end; ++r) {
-    const int seg = segment_of_token[r];
-    if (seg < 0) continue;
-    const int s = LSE_CHECKED(seg, 0, num_segments, 0, LSE_CHECK_SEGMENT);
-    const float* window = state + (size_t)LSE_CHECKED(segment_slot[s], 0, num_slots, 0, LSE_CHECK_ROW) * (taps - 1) * channels;
-    float y = sc_conv<TD>(proj, n_partials, partial_stride, ld, off, weight, window, channels, taps, r, r - segment_start[s], c) + b;
-    if (act == 1) y = y / (1.f + expf(-y));
-    out[(size_t)r * channels + c] = from_f32<TO>(y);
+  const int first = blockIdx.x * rows_per_block, end = min(tokens, first + rows_per_block);
+  if constexpr (TAPS >= 2) {
+    float w[TAPS], before[TAPS - 1];      // before[i]: the input TAPS - 1 - i rows back
+#pragma unroll
+    for (int j = 0; j < TAPS; ++j) w[j] = weight[(size_t)c * TAPS + j];
+    int held = -1;                        // the request whose inputs `before` holds
+    for (int r = first; r < end; ++r) {
+      const int seg = segment_of_token[r];
+      if (seg < 0) { held = -1; continue; }
+      if (seg != held) {
+        const int s = LSE_CHECKED(seg, 0, num_segments, 0, LSE_CHECK_SEGMENT);
+        const float* window = state + (size_t)LSE_CHECKED(segment_slot[s], 0, num_slots, 0, LSE_CHECK_ROW) * (TAPS - 1) * channels;
+        const int l = r - segment_start[s];
+#pragma unroll
+        for (int i = 0; i < TAPS - 1; ++i) {
+          const int back = TAPS - 1 - i;
+          before[i] = l - back >= 0 ? sc_load(proj + (size_t)(r - back) * ld + off + c, n_partials, partial_stride)
+                                    : window[(size_t)(TAPS - 1 + l - back) * channels + c];
+        }
+        held = seg;
+      }
+      const float now = sc_load(proj + (size_t)r * ld + off + c, n_partials, partial_stride);
+      float y = 0.f;
+#pragma unroll
+      for (int j = 0; j < TAPS - 1; ++j) y = fmaf(w[j], before[j], y);
+      y = fmaf(w[TAPS - 1], now, y) + b;
+#pragma unroll
+      for (int i = 0; i + 1 < TAPS - 1; ++i) before[i] = before[i + 1];
+      before[TAPS - 2] = now;
+      if (act == 1) y = y / (1.f + expf(-y));
+      out[(size_t)r * channels + c] = from_f32<TO>(y);
+    }
+  } else {
+    for (int r = first; r < end; ++r) {
+      const int seg = segment_of_token[r];
+      if (seg < 0) continue;
+      const int s = LSE_CHECKED(seg, 0, num_segments, 0, LSE_CHECK_SEGMENT);
+      const float* window = state + (size_t)LSE_CHECKED(segment_slot[s], 0, num_slots, 0, LSE_CHECK_ROW) * (taps - 1) * channels;
+      float y = sc_conv<TD, 0>(proj, n_partials, partial_stride, ld, off, weight, window, channels, taps, r, r - segment_start[s], c) + b;
+      if (act == 1) y = y / (1.f + expf(-y));
+      out[(size_t)r * channels + c] = from_f32<TO>(y);
+    }
   }
 }
 
@@ -96,7 +134,7 @@ short_conv_state_kernel(const TD* __restrict__ proj, int n_partials, long long p
 
 // One block per row (256 to 1024 threads).  Channels: q (n_q * dk), then k (n_kv * dk), then v (n_kv * dv), consecutive columns from `off`,
 // with their convolution weights stacked the same way; the gate's n_q columns start at g_off.
-template <typename TD, typename TO>
+template <typename TD, typename TO, int TAPS>
 __global__ void __launch_bounds__(1024)
 conv_qk_norm_rope_kernel(const TD* __restrict__ proj, int n_partials, long long partial_stride, long long ld, int off,
                          int g_off, const float* __restrict__ weight, const float* __restrict__ state,
@@ -124,7 +162,7 @@ conv_qk_norm_rope_kernel(const TD* __restrict__ proj, int n_partials, long long 
   const int l = r - segment_start[s];
   float sq_q = 0.f, sq_k = 0.f;
   for (int c = threadIdx.x; c < channels; c += blockDim.x) {
-    const float y = sc_conv<TD>(proj, n_partials, partial_stride, ld, off, weight, window, channels, taps, r, l, c);
+    const float y = sc_conv<TD, TAPS>(proj, n_partials, partial_stride, ld, off, weight, window, channels, taps, r, l, c);
     conv[c] = y;
     if (c < q_width) sq_q = fmaf(y, y, sq_q);
     else if (c < q_width + k_width) sq_k = fmaf(y, y, sq_k);
@@ -197,14 +235,22 @@ extern "C" int lse_short_conv_act(const void* proj, int proj_dtype, int n_partia
                                   int num_segments, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (channels <= 0 || taps < 1 || n_partials < 1 || (channels + 255) / 256 > 65535) return LSE_ERR_BAD_ARGUMENT;
-  const int rows_per_block = tokens >= 1024 ? 8 : 1;
+  const int rows_per_block = tokens >= 1024 ? 16 : 1;
   const dim3 grid((tokens + rows_per_block - 1) / rows_per_block, (channels + 255) / 256);
-#define LSE_SC_CASE(TD, TO)                                                                                         \
-  lse_launch(short_conv_act_kernel<TD, TO>, grid, 256, 0, stream, (const TD*)proj, n_partials, partial_stride, ld, off, \
-             weight, bias, state, segment_of_token, segment_start, segment_slot, (TO*)out, tokens, rows_per_block,   \
-             channels, taps, act, num_slots, num_segments)
+#define LSE_SC_TAPS(TD, TO, TAPS)                                                                                   \
+  lse_launch(short_conv_act_kernel<TD, TO, TAPS>, grid, 256, 0, stream, (const TD*)proj, n_partials, partial_stride, \
+             ld, off, weight, bias, state, segment_of_token, segment_start, segment_slot, (TO*)out, tokens,          \
+             rows_per_block, channels, taps, act, num_slots, num_segments)
+#define LSE_SC_CASE(TD, TO)                          \
+  do {                                               \
+    if (taps == 4) LSE_SC_TAPS(TD, TO, 4);           \
+    else if (taps == 3) LSE_SC_TAPS(TD, TO, 3);      \
+    else if (taps == 2) LSE_SC_TAPS(TD, TO, 2);      \
+    else LSE_SC_TAPS(TD, TO, 0);                     \
+  } while (0)
   LSE_SC_TYPES(LSE_SC_CASE)
 #undef LSE_SC_CASE
+#undef LSE_SC_TAPS
   LSE_LAUNCH_CHECK();
 }
 
@@ -248,17 +294,25 @@ extern "C" int lse_conv_qk_norm_rope(const void* proj, int proj_dtype, int n_par
   // as a block has, many rows share the SMs
   const int width = (n_q + n_kv) * dk + n_kv * dv;
   const int threads = tokens <= 64 ? min(1024, (width + 31) / 32 * 32) : min(512, (width + 31) / 32 * 32);
-#define LSE_SC_CASE(TD, TO)                                                                                          \
+#define LSE_SC_TAPS(TD, TO, TAPS)                                                                                    \
   do {                                                                                                               \
     if (smem > 48 * 1024)                                                                                            \
-      cudaFuncSetAttribute(conv_qk_norm_rope_kernel<TD, TO>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-    lse_launch(conv_qk_norm_rope_kernel<TD, TO>, tokens, threads, smem, stream, (const TD*)proj, n_partials,         \
+      cudaFuncSetAttribute(conv_qk_norm_rope_kernel<TD, TO, TAPS>, cudaFuncAttributeMaxDynamicSharedMemorySize,      \
+                           (int)smem);                                                                               \
+    lse_launch(conv_qk_norm_rope_kernel<TD, TO, TAPS>, tokens, threads, smem, stream, (const TD*)proj, n_partials,   \
                partial_stride, ld, off, g_off, weight, state, q_norm, k_norm, eps, freq, rot_factor, rot_dims,       \
                positions, segment_of_token, segment_start, segment_slot, slot_mapping, (TO*)q_out, (TO*)k_cache,     \
                (TO*)v_cache, gate_out, n_q, n_kv, dk, dv, taps, page_size, num_pages, num_slots, num_segments);      \
   } while (0)
+#define LSE_SC_CASE(TD, TO)                          \
+  do {                                               \
+    if (taps == 4) LSE_SC_TAPS(TD, TO, 4);           \
+    else if (taps == 3) LSE_SC_TAPS(TD, TO, 3);      \
+    else LSE_SC_TAPS(TD, TO, 0);                     \
+  } while (0)
   LSE_SC_TYPES(LSE_SC_CASE)
 #undef LSE_SC_CASE
+#undef LSE_SC_TAPS
   LSE_LAUNCH_CHECK();
 }
 

@@ -589,9 +589,9 @@ def fororax_config(width: int, heads: int, ff: int, vocab: int = 32768, context:
 def tufevik_config(width: int, heads: int, ff: int, vocab: int = 32768, context: int = 4096) -> dict:
     dense = {"kind": "dense", "ff": ff}
     mixture = {"kind": "moe", "router": {"experts": 8, "top": 2}, "expert": {"ff": ff // 2}}
-    memory = {"heads": heads, "dim": 128, "vdim": 128, "gate_cap": 15.0}
+    memory = {"heads": heads, "dim": 128, "vdim": 128, "gate_cap": 12.0}
     left = {"heads": heads, "kv_heads": max(2, heads // 8), "dim": 128, "vdim": 128, "conv": 4, "scale": 128 ** -0.5,
-            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 1024, "fast": 32.0, "slow": 1.0}}}
+            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 1.0}}}
     right = {"inner": width, "state": 16, "dt_rank": width // 16, "conv": 4}
     side_by_side = {"left": left, "right": right, "left_scale": 0.5, "right_scale": 0.5}
     layers = [{"type": "mlstm", "mixer": memory, "mlp": dense}, {"type": "parallel", "mixer": side_by_side, "mlp": mixture},

@@ -65,9 +65,9 @@ def _tufevik_stand_in(vocab_size: int) -> dict:
     """A small model of the Tufevik design: a matrix-memory layer with a dense feed-forward, a layer with attention and
     a selective scan side by side over a mixture of experts, a matrix-memory layer over a mixture."""
     mlp = {"kind": "moe", "router": {"experts": 6, "top": 2}, "expert": {"ff": 96}}
-    memory = {"heads": 4, "dim": 32, "vdim": 32, "gate_cap": 15.0}
+    memory = {"heads": 4, "dim": 32, "vdim": 32, "gate_cap": 12.0}
     left = {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "conv": 4, "scale": 32 ** -0.5,
-            "rot": {"base": 10000.0, "dims": 16, "scaling": {"factor": 4.0, "original": 256, "fast": 32.0, "slow": 1.0}}}
+            "rot": {"base": 10000.0, "dims": 16, "scaling": {"factor": 4.0, "original": 256, "fast": 16.0, "slow": 1.0}}}
     right = {"inner": 128, "state": 16, "dt_rank": 8, "conv": 4}
     return {"architecture": "Tufevik", "vocab": vocab_size, "width": 128, "norm": {"eps": 1e-6},
             "embedding": {"scale": 128 ** 0.5}, "max_position_embeddings": 1024,

@@ -122,3 +122,12 @@ def test_the_softmax_over_the_chosen_logits_only():
     for t in range(6):
         assert set(chosen[t].tolist()) == set(logits[t].argsort(descending=True)[:3].tolist())
         assert torch.allclose(weights[t], torch.softmax(logits[t][chosen[t]], dim=-1))
+
+
+def test_the_command_line_has_a_stand_in_of_the_design():
+    from llm_serving_engine_b200.cli import tiny_config
+    from llm_serving_engine_b200.config import load_config
+
+    _, _, spec = load_config(tiny_config(300, "tufevik"))
+    assert spec.architecture == "Tufevik" and spec.vocab_size == 300 and len(spec.layers) == 3
+    assert [layer.mixer.kind for layer in spec.layers] == ["mlstm", "parallel_mixers", "mlstm"]

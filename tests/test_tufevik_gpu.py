@@ -595,3 +595,33 @@ def test_router_weights_are_the_softmax_over_the_chosen_logits(experts, top):
     if top < experts:
         over_all = torch.softmax(full, dim=-1) * (want > 0)
         assert float((over_all - want).abs().max()) > 0.01
+
+
+def test_command_line_generates_from_a_model_folder_and_from_the_stand_in():
+    """``bin/llmserve generate`` on a folder of the design (the class comes from config.json): the greedy tokens are the
+    plain implementation's; and on the random stand-in of the design."""
+    import os
+    import subprocess
+    import sys
+
+    root = str(Path(__file__).resolve().parent.parent)
+    env = dict(os.environ, PYTHONPATH=root)
+    name, prompt, count = "both_kinds", [5, 17, 3, 150, 99, 42, 7], 8
+    out = subprocess.run([sys.executable, os.path.join(root, "bin", "llmserve"), "generate", "--model", str(folder_of(name)),
+                          "--dtype", "float32", "--prompt-ids", " ".join(map(str, prompt)), "--max-new-tokens", str(count)],
+                         capture_output=True, text=True, env=env, timeout=600)
+    assert out.returncode == 0, out.stderr
+    tokens = json.loads(out.stdout.strip().splitlines()[-1])["output_ids"]
+    assert len(tokens) == count
+    logits = reference(name, prompt + tokens)
+    for index, token in enumerate(tokens):
+        row = logits[len(prompt) + index - 1]
+        top = torch.topk(row, 2).values
+        if float(top[0] - top[1]) < 1e-3 * float(row.abs().max()):
+            break
+        assert int(row.argmax()) == token, f"token {index}"
+    out = subprocess.run([sys.executable, os.path.join(root, "bin", "llmserve"), "generate", "--random", "tufevik",
+                          "--prompt-ids", "5 17 3 250 99", "--max-new-tokens", "6"],
+                         capture_output=True, text=True, env=env, timeout=600)
+    assert out.returncode == 0, out.stderr
+    assert len(json.loads(out.stdout.strip().splitlines()[-1])["output_ids"]) == 6

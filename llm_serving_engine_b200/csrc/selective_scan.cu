@@ -19,7 +19,7 @@ LSE_CHECK_DEFINE(lse_check_selective_scan)
 
 namespace {
 constexpr int SS_THREADS = 128;
-constexpr int SS_PER_LANE = 4;     // states a thread keeps
+constexpr int SS_PER_LANE = 4;     // states a thread keeps (one 16-byte read of a token's B and of its C)
 constexpr int SS_TOKENS = 16;      // tokens staged at a time
 
 template <typename TD>
@@ -104,7 +104,8 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt, co
                       int channels, int states, int num_slots, int num_segments, int chunk_rows, int phase,
                       float* __restrict__ chunk_state, float* __restrict__ chunk_dt) {
   constexpr int CH = SS_THREADS / LANES;     // channels of a block
-  extern __shared__ float ss_smem[];         // [16][states] B, [16][states] C, [16][CH] dt, x, z
+  constexpr int SP = LANES * SS_PER_LANE;    // a token's B (or C) in shared memory: the states, then zeros up to a lane's four
+  extern __shared__ __align__(16) float ss_smem[];   // [16][SP] B, [16][SP] C, [16][CH] dt, x, z
   __shared__ int item[3];
   pdl_launch_dependents();
   pdl_wait();
@@ -137,8 +138,8 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt, co
   const bool outputs = !from_zero;
   const bool store = !(chunk_rows > 0 && phase == 2);
   float* b_s = ss_smem;
-  float* c_s = b_s + SS_TOKENS * states;
-  float* dt_s = c_s + SS_TOKENS * states;
+  float* c_s = b_s + SS_TOKENS * SP;
+  float* dt_s = c_s + SS_TOKENS * SP;
   float* x_s = dt_s + SS_TOKENS * CH;
   float* z_s = x_s + SS_TOKENS * CH;
   const int sub = threadIdx.x % LANES, local = threadIdx.x / LANES;
@@ -150,7 +151,7 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt, co
   float s[SS_PER_LANE], a[SS_PER_LANE];
 #pragma unroll
   for (int i = 0; i < SS_PER_LANE; ++i) {
-    const int n = i * LANES + sub;          // lanes of a channel read neighbouring states
+    const int n = sub * SS_PER_LANE + i;    // a lane's four states lie side by side: one 16-byte read of B and of C a token
     const bool has = live && n < states;
     s[i] = has && !from_zero ? st[n] : 0.f;
     a[i] = has ? -expf(a_log[(size_t)c * states + n]) : 0.f;
@@ -160,11 +161,11 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt, co
   for (int base = row0; base < row1; base += SS_TOKENS) {
     const int n_tok = min(SS_TOKENS, row1 - base);
     __syncthreads();
-    for (int e = threadIdx.x; e < n_tok * states; e += SS_THREADS) {
-      const int t = e / states, n = e % states;
+    for (int e = threadIdx.x; e < n_tok * SP; e += SS_THREADS) {
+      const int t = e / SP, n = e % SP;
       const TL* row = low + (size_t)(base + t) * low_ld;
-      b_s[t * states + n] = ss_load(row + b_off + n, low_partials, low_stride);
-      if (outputs) c_s[t * states + n] = ss_load(row + c_off + n, low_partials, low_stride);
+      b_s[e] = n < states ? ss_load(row + b_off + n, low_partials, low_stride) : 0.f;
+      if (outputs) c_s[e] = n < states ? ss_load(row + c_off + n, low_partials, low_stride) : 0.f;
     }
     for (int e = threadIdx.x; e < n_tok * CH; e += SS_THREADS) {
       const int t = e / CH, cc = blockIdx.y * CH + e % CH;
@@ -179,11 +180,10 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt, co
         const float step = dt_s[t * CH + local];
         const float push = step * x_s[t * CH + local];
         dt_sum += step;
+        const float4 b4 = *reinterpret_cast<const float4*>(b_s + t * SP + sub * SS_PER_LANE);
+        const float bv[SS_PER_LANE] = {b4.x, b4.y, b4.z, b4.w};
 #pragma unroll
-        for (int i = 0; i < SS_PER_LANE; ++i) {
-          const int n = i * LANES + sub;
-          if (n < states) s[i] = fmaf(expf(step * a[i]), s[i], push * b_s[t * states + n]);
-        }
+        for (int i = 0; i < SS_PER_LANE; ++i) s[i] = fmaf(expf(step * a[i]), s[i], push * bv[i]);   // past the last state: 1 * 0 + push * 0
       }
       continue;
     }
@@ -191,13 +191,13 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt, co
       const float step = dt_s[t * CH + local], xv = x_s[t * CH + local];
       const float push = step * xv;
       float y = 0.f;
+      const float4 b4 = *reinterpret_cast<const float4*>(b_s + t * SP + sub * SS_PER_LANE);
+      const float4 c4 = *reinterpret_cast<const float4*>(c_s + t * SP + sub * SS_PER_LANE);
+      const float bv[SS_PER_LANE] = {b4.x, b4.y, b4.z, b4.w}, cv[SS_PER_LANE] = {c4.x, c4.y, c4.z, c4.w};
 #pragma unroll
       for (int i = 0; i < SS_PER_LANE; ++i) {
-        const int n = i * LANES + sub;
-        if (n < states) {
-          s[i] = fmaf(expf(step * a[i]), s[i], push * b_s[t * states + n]);
-          y = fmaf(s[i], c_s[t * states + n], y);
-        }
+        s[i] = fmaf(expf(step * a[i]), s[i], push * bv[i]);
+        y = fmaf(s[i], cv[i], y);
       }
 #pragma unroll
       for (int o = 1; o < LANES; o <<= 1) y += __shfl_xor_sync(0xffffffffu, y, o);
@@ -211,7 +211,7 @@ selective_scan_kernel(const TX* __restrict__ x, const float* __restrict__ dt, co
   if (live && store) {
 #pragma unroll
     for (int i = 0; i < SS_PER_LANE; ++i) {
-      const int n = i * LANES + sub;
+      const int n = sub * SS_PER_LANE + i;
       if (n < states) st[n] = s[i];
     }
     if (from_zero && sub == 0) chunk_dt[(size_t)blockIdx.x * channels + c] = dt_sum;
@@ -314,7 +314,7 @@ extern "C" int lse_selective_scan(const void* x, int x_dtype, const float* dt, c
 #define LSE_SS_LAUNCH(TD, TL, TX, TO, L)                                                                           \
   {                                                                                                                \
     constexpr int ch = SS_THREADS / L;                                                                             \
-    const size_t smem = sizeof(float) * SS_TOKENS * (2 * (size_t)states + 3 * ch);                                 \
+    const size_t smem = sizeof(float) * SS_TOKENS * (2 * (size_t)L * SS_PER_LANE + 3 * ch);                                 \
     const dim3 grid(chunk_rows > 0 ? max_chunks : max_segments, (channels + ch - 1) / ch);                         \
     for (int phase = 1; phase <= (chunk_rows > 0 ? 2 : 1); ++phase) {                                              \
       lse_launch(selective_scan_kernel<TD, TL, TX, TO, L>, grid, SS_THREADS, smem, stream, (const TX*)x, dt,       \

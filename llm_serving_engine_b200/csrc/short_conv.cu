@@ -181,10 +181,13 @@ conv_qk_norm_rope_kernel(const TD* __restrict__ proj, int n_partials, long long 
   const float inv_k = 1.0f / sqrtf(block_sum(sq_k, scratch) / (float)k_width + eps);
   const int slot = LSE_CHECKED(slot_mapping[r], 0, num_pages * page_size, -1, LSE_CHECK_CACHE_SLOT);
   const int page = slot >= 0 ? slot / page_size : 0, place = slot >= 0 ? slot % page_size : 0;
-  // q and k: normed over the whole projection, then rotated head by head
+  // q and k: normed over the whole projection, then rotated head by head.  A head's size is a power of two in most
+  // models: a shift and a mask then take the place of the division.
+  const int dk_shift = (dk & (dk - 1)) == 0 ? __ffs(dk) - 1 : -1, dv_shift = (dv & (dv - 1)) == 0 ? __ffs(dv) - 1 : -1;
   for (int c = threadIdx.x; c < q_width + k_width; c += blockDim.x) {
     const bool is_q = c < q_width;
-    const int local = is_q ? c : c - q_width, head = local / dk, i = local % dk;
+    const int local = is_q ? c : c - q_width;
+    const int head = dk_shift >= 0 ? local >> dk_shift : local / dk, i = dk_shift >= 0 ? local & (dk - 1) : local % dk;
     const float* norm = is_q ? q_norm : k_norm;
     const float inv = is_q ? inv_q : inv_k;
     float y = conv[c] * inv * norm[local];
@@ -198,8 +201,10 @@ conv_qk_norm_rope_kernel(const TD* __restrict__ proj, int n_partials, long long 
     else if (slot >= 0) k_cache[(((size_t)page * n_kv + head) * page_size + place) * dk + i] = from_f32<TO>(y);
   }
   if (slot >= 0)
-    for (int c = threadIdx.x; c < v_width; c += blockDim.x)
-      v_cache[(((size_t)page * n_kv + c / dv) * page_size + place) * dv + c % dv] = from_f32<TO>(conv[q_width + k_width + c]);
+    for (int c = threadIdx.x; c < v_width; c += blockDim.x) {
+      const int head = dv_shift >= 0 ? c >> dv_shift : c / dv, i = dv_shift >= 0 ? c & (dv - 1) : c % dv;
+      v_cache[(((size_t)page * n_kv + head) * page_size + place) * dv + i] = from_f32<TO>(conv[q_width + k_width + c]);
+    }
 }
 
 template <typename TI, typename TO>

@@ -68,12 +68,34 @@ def load_config(folder_or_dict) -> tuple[Architecture, Any, ModelSpec]:
             raise ConfigError(f"no config.json at {path}")
         values = json.loads(path.read_text())
     entry = resolve_architecture(values)
-    names = None if isinstance(folder_or_dict, dict) else _checkpoint_tensor_names(Path(folder_or_dict))
-    if names is not None and "tensor_names" in inspect.signature(entry.config_class.from_dict).parameters:
+    accepted = inspect.signature(entry.config_class.from_dict).parameters
+    shapes = None
+    if not isinstance(folder_or_dict, dict) and "tensor_shapes" in accepted:
+        shapes = _checkpoint_tensor_shapes(Path(folder_or_dict))
+    names = None if isinstance(folder_or_dict, dict) or shapes is not None else _checkpoint_tensor_names(Path(folder_or_dict))
+    if shapes is not None:
+        config = entry.config_class.from_dict(values, tensor_shapes=shapes)   # a design some of whose sizes only the tensors give
+    elif names is not None and "tensor_names" in accepted:
         config = entry.config_class.from_dict(values, tensor_names=names)   # a design whose file leaves to the tensors what it has
     else:
         config = entry.config_class.from_dict(values)
     return entry, config, entry.build_spec(config)
+
+
+def _checkpoint_tensor_shapes(folder: Path):
+    """name -> shape of the tensors in the safetensors files beside config.json (None when there are none)."""
+    folder = folder if folder.is_dir() else folder.parent
+    files = sorted(folder.glob("*.safetensors"))
+    if not files:
+        return None
+    from safetensors import safe_open
+
+    shapes: dict[str, tuple] = {}
+    for filename in files:
+        with safe_open(str(filename), framework="pt", device="cpu") as source:
+            for name in source.keys():
+                shapes[name] = tuple(source.get_slice(name).get_shape())
+    return shapes
 
 
 def _checkpoint_tensor_names(folder: Path):

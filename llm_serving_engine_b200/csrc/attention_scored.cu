@@ -10,6 +10,13 @@
 //     weights, so it is taken after the softmax has been normalised (sink included) without ever holding a
 //     [heads, keys] tile of weights.  `lse_head_mix_gate` does that sum and multiplies by an elementwise gate.
 //
+//   * window: row i reads keys j with i - j < window only (window <= 0: every key up to i); pages before the window
+//     are never touched (their table entries may have been given back);
+//   * cap: s <- cap * tanh(s / cap) before anything else is done with the score (cap <= 0: none);
+//   * weights without a softmax (`head_bias` given): a key's weight is sigmoid(s_ij + head_bias_h), not normalised
+//     over the keys; the output is the plain weighted sum of the values.  The chunks' sums are then added in order
+//     (the running maximum stays 0 and the denominator is not used).
+//
 // Keys are walked in tiles of KT with the online-softmax recurrence, chunk by chunk (CHUNK keys, counted from key 0);
 // the chunks' (max, sum, acc) are merged in order.  With few rows every chunk has a block of its own and a second
 // kernel merges them with the same operations in the same order.  Chunks and tiles depend on the row's own position
@@ -54,7 +61,8 @@ attention_scored_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
                         const int* __restrict__ segment_of_token, const int* __restrict__ positions,
                         const float* __restrict__ r1, const float* __restrict__ r2, const float* __restrict__ sink,
                         int n_q, int n_kv, int dk, int dv, int n_values, int page_size, float scale, int num_pages,
-                        int num_segments, float* __restrict__ partials, int max_chunks) {
+                        int num_segments, float* __restrict__ partials, int max_chunks, int window, float cap,
+                        const float* __restrict__ head_bias) {
   extern __shared__ float smem[];
   pdl_launch_dependents();
   pdl_wait();
@@ -73,9 +81,10 @@ attention_scored_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
   if (seg < 0) return;
   const int pos = positions[t];
   const int ctx = pos + 1;
-  int chunk_lo = 0, chunk_hi = pos / CHUNK;
+  const int first_key = window > 0 ? max(0, ctx - window) : 0;   // the first key the row reads
+  int chunk_lo = first_key / CHUNK, chunk_hi = pos / CHUNK;
   if (SPLIT) {
-    if (zz > chunk_hi) return;
+    if (zz > chunk_hi || zz < chunk_lo) return;
     chunk_lo = chunk_hi = zz;
   }
   const int* bt = block_tables + (size_t)seg * bt_stride;
@@ -105,13 +114,15 @@ attention_scored_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     for (int i = 0; i < DPT; ++i) total[g][i] = 0.f;
   }
   // the penalty's constants of the heads this warp scores (g = warp, warp + 4)
-  float pen1[GC / 4], pen2[GC / 4];
+  float pen1[GC / 4], pen2[GC / 4], hb[GC / 4];
 #pragma unroll
   for (int i = 0; i < GC / 4; ++i) {
     const int g = warp + 4 * i;
     pen1[i] = (r1 && g < gcount) ? r1[first_head + g] : 0.f;
     pen2[i] = (r2 && g < gcount) ? r2[first_head + g] : 0.f;
+    hb[i] = (head_bias && g < gcount) ? head_bias[first_head + g] : 0.f;
   }
+  const float inv_cap = cap > 0.f ? 1.0f / cap : 0.f;
 
   for (int chunk = chunk_lo; chunk <= chunk_hi; ++chunk) {
     float acc[GC][DPT];
@@ -124,12 +135,12 @@ attention_scored_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     for (int i = 0; i < GC / 4; ++i) { m_run[i] = -INFINITY; l_run[i] = 0.f; }
 
     const int tile_end = min(ctx, (chunk + 1) * CHUNK);
-    for (int base = chunk * CHUNK; base < tile_end; base += KT) {
+    for (int base = max(chunk * CHUNK, first_key / KT * KT); base < tile_end; base += KT) {
       __syncthreads();  // previous tile fully consumed (also orders the q_s fill)
       if (tid < KT) {
         const int j = base + tid;
         int slot = -1;
-        if (j < ctx) {
+        if (j < ctx && j >= first_key) {
           const int page = LSE_CHECKED(bt[j / page_size], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY);
           slot = page * page_size + (j % page_size);
         }
@@ -167,11 +178,19 @@ attention_scored_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
           const float* kr = k_s + lane * (dk + 1);
           for (int d = 0; d < dk; ++d) s = fmaf(qr[d], kr[d], s);
           s *= scale;
+          if (cap > 0.f) s = cap * tanhf(s * inv_cap);
           if (r1) s -= pen1[i] * log1pf(pen2[i] * (float)(pos - (base + lane)));
           s = valid ? s : -INFINITY;
-          const float m_new = fmaxf(m_run[i], warp_max(s));
-          const float c = expf(m_run[i] - m_new);  // exp(-inf) = 0 on the first tile
-          const float p = valid ? expf(s - m_new) : 0.f;
+          float m_new, c, p;
+          if (head_bias) {   // no softmax: the weight is the sigmoid of the score itself
+            m_new = 0.f;
+            c = m_run[i] == 0.f ? 1.f : 0.f;
+            p = valid ? 1.0f / (1.0f + expf(-(s + hb[i]))) : 0.f;
+          } else {
+            m_new = fmaxf(m_run[i], warp_max(s));
+            c = expf(m_run[i] - m_new);  // exp(-inf) = 0 on the first tile
+            p = valid ? expf(s - m_new) : 0.f;
+          }
           p_s[g * KT + lane] = p;
           float tile_sum = 0.f;  // keys in order, the same in every lane
           for (int j = 0; j < KT; ++j) tile_sum += __shfl_sync(0xffffffffu, p, j);
@@ -228,6 +247,7 @@ attention_scored_kernel(const T* __restrict__ q, const T* __restrict__ k_cache, 
     if (g < gcount) {
       float l = L[g];
       const float w = sink ? add_sink(M[g], l, sink[first_head + g]) : 1.f;
+      if (head_bias) l = 1.f;
 #pragma unroll
       for (int i = 0; i < DPT; ++i) {
         const int d = tid + i * THREADS;
@@ -243,7 +263,8 @@ template <typename TO>
 __global__ void __launch_bounds__(MAX_D)
 attention_scored_merge_kernel(const float* __restrict__ partials, TO* __restrict__ out,
                               const int* __restrict__ segment_of_token, const int* __restrict__ positions,
-                              const float* __restrict__ sink, int n_values, int dv, int max_chunks, int num_segments) {
+                              const float* __restrict__ sink, int n_values, int dv, int max_chunks, int num_segments,
+                              int window, int unnormalised) {
   pdl_launch_dependents();
   pdl_wait();
   const int t = blockIdx.x, item = blockIdx.y, d = threadIdx.x;
@@ -252,13 +273,15 @@ attention_scored_merge_kernel(const float* __restrict__ partials, TO* __restrict
   const int pos = positions[t];
   const float* src = partials + ((size_t)t * gridDim.y + item) * max_chunks * (dv + 2);
   float total = 0.f, M = -INFINITY, L = 0.f;
-  for (int chunk = 0; chunk <= pos / CHUNK; ++chunk) {
+  const int first_chunk = window > 0 ? max(0, pos + 1 - window) / CHUNK : 0;
+  for (int chunk = first_chunk; chunk <= pos / CHUNK; ++chunk) {
     const float* part = src + (size_t)chunk * (dv + 2);
     float wa, wb;
     merge_parts(M, L, part[dv], part[dv + 1], wa, wb);
     total = fmaf(part[d], wb, total * wa);
   }
   const float w = sink ? add_sink(M, L, sink[item / n_values]) : 1.f;
+  if (unnormalised) L = 1.f;
   out[((size_t)t * gridDim.y + item) * dv + d] = from_f32<TO>(total * w / L);
 }
 
@@ -388,7 +411,8 @@ template <typename T, typename TO>
 int launch_scored(const void* q, const void* k_cache, const void* v_cache, void* out, const int* block_tables,
                   int bt_stride, const int* segment_of_token, const int* positions, const float* r1, const float* r2,
                   const float* sink, int tokens, int n_q, int n_kv, int dk, int dv, int n_values, int page_size,
-                  float scale, int num_pages, int num_segments, float* partials, int max_chunks, cudaStream_t stream) {
+                  float scale, int num_pages, int num_segments, float* partials, int max_chunks, int window, float cap,
+                  const float* head_bias, cudaStream_t stream) {
   const int group = n_q / n_kv;
   const int gchunks = (group + GC - 1) / GC;
   const bool split = partials != nullptr;
@@ -407,14 +431,14 @@ int launch_scored(const void* q, const void* k_cache, const void* v_cache, void*
   if (split) {
     lse_launch(attention_scored_kernel<T, TO, true>, grid, THREADS, smem, stream, (const T*)q, (const T*)k_cache,
                (const T*)v_cache, (TO*)out, block_tables, bt_stride, segment_of_token, positions, r1, r2, sink, n_q, n_kv,
-               dk, dv, n_values, page_size, scale, num_pages, num_segments, partials, max_chunks);
+               dk, dv, n_values, page_size, scale, num_pages, num_segments, partials, max_chunks, window, cap, head_bias);
     lse_launch(attention_scored_merge_kernel<TO>, dim3(tokens, n_q * n_values), ((dv + 31) / 32) * 32, 0, stream,
                (const float*)partials, (TO*)out, segment_of_token, positions, sink, n_values, dv, max_chunks,
-               num_segments);
+               num_segments, window, (int)(head_bias != nullptr));
   } else {
     lse_launch(attention_scored_kernel<T, TO, false>, grid, THREADS, smem, stream, (const T*)q, (const T*)k_cache,
                (const T*)v_cache, (TO*)out, block_tables, bt_stride, segment_of_token, positions, r1, r2, sink, n_q, n_kv,
-               dk, dv, n_values, page_size, scale, num_pages, num_segments, (float*)nullptr, 0);
+               dk, dv, n_values, page_size, scale, num_pages, num_segments, (float*)nullptr, 0, window, cap, head_bias);
   }
   return (int)cudaGetLastError();
 }
@@ -426,13 +450,17 @@ extern "C" int lse_attention_scored_chunk(void) { return CHUNK; }
 // cross != 0: n_values = n_kv (see the top of the file), else 1.  r1/r2 (together) and sink: float32 [n_q] or null.
 // partials != null: every chunk of a row gets a block of its own; it holds tokens * n_q * n_values * max_chunks *
 // (dv + 2) floats, and max_chunks chunks cover the longest context that the block tables can describe.
-extern "C" int lse_attention_scored(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
-                                    int out_f32, const int* block_tables, int bt_stride, const int* segment_of_token,
-                                    const int* positions, const float* r1, const float* r2, const float* sink,
-                                    int tokens, int n_q, int n_kv, int dk, int dv, int cross, int page_size, float scale,
-                                    int num_pages, int num_segments, float* partials, int max_chunks,
-                                    cudaStream_t stream) {
+// window > 0: a row reads its last `window` keys only; cap > 0: scores capped by cap * tanh(s / cap); head_bias (float32
+// [n_q] or null): weights sigmoid(s + head_bias_h) without a softmax (no sink then).
+extern "C" int lse_attention_scored_windowed(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
+                                             int out_f32, const int* block_tables, int bt_stride,
+                                             const int* segment_of_token, const int* positions, const float* r1,
+                                             const float* r2, const float* sink, int tokens, int n_q, int n_kv, int dk,
+                                             int dv, int cross, int page_size, float scale, int num_pages,
+                                             int num_segments, float* partials, int max_chunks, int window, float cap,
+                                             const float* head_bias, cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  if (head_bias && sink) return LSE_ERR_BAD_ARGUMENT;
   if (dk <= 0 || dk > MAX_D || dv <= 0 || dv > MAX_D || n_kv <= 0 || n_q % n_kv || page_size <= 0 || (!r1) != (!r2))
     return LSE_ERR_BAD_ARGUMENT;
   const int n_values = cross ? n_kv : 1;
@@ -442,7 +470,7 @@ extern "C" int lse_attention_scored(const void* q, const void* k_cache, const vo
   if ((long long)(partials ? max_chunks : 1) * n_values * gchunks > 65535 || n_kv > 65535 || n_q * n_values > 65535)
     return LSE_ERR_TOO_LARGE;
 #define LSE_SCORED_ARGS q, k_cache, v_cache, out, block_tables, bt_stride, segment_of_token, positions, r1, r2, sink, tokens, \
-  n_q, n_kv, dk, dv, n_values, page_size, scale, num_pages, num_segments, partials, max_chunks, stream
+  n_q, n_kv, dk, dv, n_values, page_size, scale, num_pages, num_segments, partials, max_chunks, window, cap, head_bias, stream
   if (dtype == LSE_DTYPE_F32) return launch_scored<float, float>(LSE_SCORED_ARGS);
   if (dtype == LSE_DTYPE_BF16 && out_f32) return launch_scored<__nv_bfloat16, float>(LSE_SCORED_ARGS);
   if (dtype == LSE_DTYPE_BF16) return launch_scored<__nv_bfloat16, __nv_bfloat16>(LSE_SCORED_ARGS);
@@ -450,24 +478,44 @@ extern "C" int lse_attention_scored(const void* q, const void* k_cache, const vo
   return LSE_ERR_BAD_ARGUMENT;
 }
 
+extern "C" int lse_attention_scored(const void* q, const void* k_cache, const void* v_cache, void* out, int dtype,
+                                    int out_f32, const int* block_tables, int bt_stride, const int* segment_of_token,
+                                    const int* positions, const float* r1, const float* r2, const float* sink,
+                                    int tokens, int n_q, int n_kv, int dk, int dv, int cross, int page_size, float scale,
+                                    int num_pages, int num_segments, float* partials, int max_chunks,
+                                    cudaStream_t stream) {
+  return lse_attention_scored_windowed(q, k_cache, v_cache, out, dtype, out_f32, block_tables, bt_stride, segment_of_token,
+                                       positions, r1, r2, sink, tokens, n_q, n_kv, dk, dv, cross, page_size, scale,
+                                       num_pages, num_segments, partials, max_chunks, 0, 0.f, nullptr, stream);
+}
+
 // The second half of a launch with partials, for kernels of other files that leave partials in the same layout
 // ([t][head][value slot][chunk][dv + 2]: sums, maximum, total): out [T, n_q, n_values, dv] in bfloat16 or float32.
-extern "C" int lse_attention_scored_merge(const float* partials, void* out, int out_dtype, const int* segment_of_token,
-                                          const int* positions, const float* sink, int tokens, int n_q, int n_values,
-                                          int dv, int max_chunks, int num_segments, cudaStream_t stream) {
+// window, unnormalised: as the launch that left the partials had them (chunks before the window hold nothing).
+extern "C" int lse_attention_scored_merge_windowed(const float* partials, void* out, int out_dtype,
+                                                   const int* segment_of_token, const int* positions, const float* sink,
+                                                   int tokens, int n_q, int n_values, int dv, int max_chunks,
+                                                   int num_segments, int window, int unnormalised, cudaStream_t stream) {
   if (tokens <= 0) return 0;
   if (dv <= 0 || dv > MAX_D || n_q * n_values > 65535 || max_chunks <= 0) return LSE_ERR_BAD_ARGUMENT;
   const dim3 grid(tokens, n_q * n_values);
   const int threads = ((dv + 31) / 32) * 32;
   if (out_dtype == LSE_DTYPE_F32)
     lse_launch(attention_scored_merge_kernel<float>, grid, threads, 0, stream, partials, (float*)out, segment_of_token,
-               positions, sink, n_values, dv, max_chunks, num_segments);
+               positions, sink, n_values, dv, max_chunks, num_segments, window, unnormalised);
   else if (out_dtype == LSE_DTYPE_BF16)
     lse_launch(attention_scored_merge_kernel<__nv_bfloat16>, grid, threads, 0, stream, partials, (__nv_bfloat16*)out,
-               segment_of_token, positions, sink, n_values, dv, max_chunks, num_segments);
+               segment_of_token, positions, sink, n_values, dv, max_chunks, num_segments, window, unnormalised);
   else
     return LSE_ERR_BAD_ARGUMENT;
   LSE_LAUNCH_CHECK();
+}
+
+extern "C" int lse_attention_scored_merge(const float* partials, void* out, int out_dtype, const int* segment_of_token,
+                                          const int* positions, const float* sink, int tokens, int n_q, int n_values,
+                                          int dv, int max_chunks, int num_segments, cudaStream_t stream) {
+  return lse_attention_scored_merge_windowed(partials, out, out_dtype, segment_of_token, positions, sink, tokens, n_q,
+                                             n_values, dv, max_chunks, num_segments, 0, 0, stream);
 }
 
 // wide [T, n_q, n_values, dv] (n_values = n_kv when cross, else 1) in float32, or in bfloat16 (wide_bf16; only shapes

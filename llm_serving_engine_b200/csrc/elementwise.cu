@@ -591,17 +591,29 @@ extern "C" int lse_rope_kv_write(const void* qkv, int in_dtype, int n_partials, 
 template <int ACT, bool FAST>
 __device__ __forceinline__ float gate_act(float g) {
   if (ACT == 2) return fmaxf(g, 0.f);
+  if (ACT == 3) return FAST ? __fdividef(g, 1.0f + __expf(-1.702f * g)) : g / (1.0f + expf(-1.702f * g));
   if (ACT == 0) return FAST ? __fdividef(g, 1.0f + __expf(-g)) : g / (1.0f + expf(-g));
   const float inner = 0.7978845608028654f * fmaf(0.044715f * g * g, g, g);
   if (FAST) return g - __fdividef(g, 1.0f + __expf(2.0f * inner));   // 0.5 g (1 + tanh x) = g - g / (1 + exp(2x))
   return 0.5f * g * (1.0f + tanhf(inner));
 }
 
+// The product of the activated gate and the up value.  ACT 3 (clamped swish): g' = min(g, limit), u' = clamp(u, -limit,
+// limit), g' sigmoid(1.702 g') (u' + 1); the others: act(g) u, `limit` not read.
+template <int ACT, bool FAST>
+__device__ __forceinline__ float gate_mul(float g, float u, float limit) {
+  if (ACT == 3) {
+    g = fminf(g, limit);
+    u = fminf(fmaxf(u, -limit), limit) + 1.0f;
+  }
+  return gate_act<ACT, FAST>(g) * u;
+}
+
 // gate_up[t] = [gate (I values) | up (I values)];  out[t, i] = silu(gate_i) * up_i
 // grid: (chunks of the row, tokens); a thread handles 4 consecutive i when I % 4 == 0.
 template <typename TI, typename TO, int VEC, int ACT>
 __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, long long partial_stride,
-                                TO* __restrict__ out, int inter) {
+                                TO* __restrict__ out, int inter, float limit) {
   LSE_TL_BEGIN(4)
   pdl_launch_dependents();
   pdl_wait();
@@ -627,8 +639,8 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, 
   float y[4];
 #pragma unroll
   for (int e = 0; e < VEC; ++e) {
-    if (sizeof(TO) == 2) y[e] = gate_act<ACT, true>(g[e]) * u[e];
-    else y[e] = gate_act<ACT, false>(g[e]) * u[e];
+    if (sizeof(TO) == 2) y[e] = gate_mul<ACT, true>(g[e], u[e], limit);
+    else y[e] = gate_mul<ACT, false>(g[e], u[e], limit);
   }
   TO* dst = out + (size_t)t * inter + i;
   if (VEC == 4) store4<TO>(dst, y);
@@ -642,7 +654,7 @@ __global__ void silu_mul_kernel(const TI* __restrict__ gate_up, int n_partials, 
 constexpr int SILU_UNROLL = 1;
 template <int ACT>
 __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up, __nv_bfloat16* __restrict__ out,
-                                       int inter, long long total_chunks) {
+                                       int inter, long long total_chunks, float limit) {
   LSE_TL_BEGIN(4)
   pdl_launch_dependents();
   pdl_wait();
@@ -674,8 +686,8 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
       const __nv_bfloat162 g2 = *reinterpret_cast<const __nv_bfloat162*>(&gw[e]);
       const __nv_bfloat162 u2 = *reinterpret_cast<const __nv_bfloat162*>(&uw[e]);
       const float ga = __low2float(g2), gb = __high2float(g2);
-      __nv_bfloat162 y = __floats2bfloat162_rn(gate_act<ACT, true>(ga) * __low2float(u2),
-                                               gate_act<ACT, true>(gb) * __high2float(u2));
+      __nv_bfloat162 y = __floats2bfloat162_rn(gate_mul<ACT, true>(ga, __low2float(u2), limit),
+                                               gate_mul<ACT, true>(gb, __high2float(u2), limit));
       yw[e] = *reinterpret_cast<uint32_t*>(&y);
     }
     *reinterpret_cast<uint4*>(out + where[k]) = make_uint4(yw[0], yw[1], yw[2], yw[3]);
@@ -685,7 +697,7 @@ __global__ void silu_mul_bf16x8_kernel(const __nv_bfloat16* __restrict__ gate_up
 
 template <int ACT>
 static int gated_act_mul_launch(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,
-                                int out_dtype, int tokens, int inter, cudaStream_t stream) {
+                                int out_dtype, int tokens, int inter, float limit, cudaStream_t stream) {
   if (tokens <= 0 || inter <= 0) return 0;
   if (n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
   const bool vec = inter % 4 == 0 && partial_stride % 4 == 0 && (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0;
@@ -694,16 +706,16 @@ static int gated_act_mul_launch(const void* gate_up, int in_dtype, int n_partial
     const long long total_chunks = (long long)tokens * (inter / 8);
     const unsigned blocks = (unsigned)((total_chunks + threads * SILU_UNROLL - 1) / (threads * SILU_UNROLL));
     lse_launch(silu_mul_bf16x8_kernel<ACT>, blocks, threads, 0, stream, (const __nv_bfloat16*)gate_up, (__nv_bfloat16*)out,
-               inter, total_chunks);
+               inter, total_chunks, limit);
     LSE_LAUNCH_CHECK();
   }
   const int per_row = vec ? inter / 4 : inter;
   dim3 grid((per_row + threads - 1) / threads, tokens);
 #define LSE_SILU_CASE(TI, TO)                                                                                      \
   if (vec) lse_launch(silu_mul_kernel<TI, TO, 4, ACT>, grid, threads, 0, stream, (const TI*)gate_up, n_partials,    \
-                      partial_stride, (TO*)out, inter);                                                            \
+                      partial_stride, (TO*)out, inter, limit);                                                     \
   else lse_launch(silu_mul_kernel<TI, TO, 1, ACT>, grid, threads, 0, stream, (const TI*)gate_up, n_partials,        \
-                  partial_stride, (TO*)out, inter)
+                  partial_stride, (TO*)out, inter, limit)
   if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) { LSE_SILU_CASE(float, float); }
   else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) { LSE_SILU_CASE(__nv_bfloat16, __nv_bfloat16); }
   else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) { LSE_SILU_CASE(float, __nv_bfloat16); }
@@ -714,19 +726,27 @@ static int gated_act_mul_launch(const void* gate_up, int in_dtype, int n_partial
 
 extern "C" int lse_silu_mul(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,
                             int out_dtype, int tokens, int inter, cudaStream_t stream) {
-  return gated_act_mul_launch<0>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, stream);
+  return gated_act_mul_launch<0>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, 0.f, stream);
 }
 
-// activation: 0 = SiLU, 1 = the tanh form of GELU, 2 = ReLU
+// activation: 0 = SiLU, 1 = the tanh form of GELU, 2 = ReLU, 3 = clamped swish (see gate_mul; the only one that reads limit)
+extern "C" int lse_gated_act_mul_limit(const void* gate_up, int in_dtype, int n_partials, long long partial_stride,
+                                       void* out, int out_dtype, int tokens, int inter, int activation, float limit,
+                                       cudaStream_t stream) {
+#define LSE_GATED_ACT_ARGS gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, limit, stream
+  if (activation == 0) return gated_act_mul_launch<0>(LSE_GATED_ACT_ARGS);
+  if (activation == 1) return gated_act_mul_launch<1>(LSE_GATED_ACT_ARGS);
+  if (activation == 2) return gated_act_mul_launch<2>(LSE_GATED_ACT_ARGS);
+  if (activation == 3) return limit > 0.f ? gated_act_mul_launch<3>(LSE_GATED_ACT_ARGS) : LSE_ERR_BAD_ARGUMENT;
+#undef LSE_GATED_ACT_ARGS
+  return LSE_ERR_BAD_ARGUMENT;
+}
+
 extern "C" int lse_gated_act_mul(const void* gate_up, int in_dtype, int n_partials, long long partial_stride, void* out,
                                  int out_dtype, int tokens, int inter, int activation, cudaStream_t stream) {
-  if (activation == 0)
-    return gated_act_mul_launch<0>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, stream);
-  if (activation == 1)
-    return gated_act_mul_launch<1>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, stream);
-  if (activation == 2)
-    return gated_act_mul_launch<2>(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, stream);
-  return LSE_ERR_BAD_ARGUMENT;
+  if (activation == 3) return LSE_ERR_BAD_ARGUMENT;
+  return lse_gated_act_mul_limit(gate_up, in_dtype, n_partials, partial_stride, out, out_dtype, tokens, inter, activation,
+                                 0.f, stream);
 }
 
 // Switch programmatic dependent launch on (1, the default) or off (0) for every later launch.

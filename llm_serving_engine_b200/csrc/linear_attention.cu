@@ -43,8 +43,16 @@ __device__ __forceinline__ float la_act(float z, int act) { return act == 1 ? z 
 //     S_t = keep[t, h] * S_(t-1) + take[t, h] * k_t v_t^T,
 // and the state has one more column, whose "value" is one for every token: it carries n_t = keep n_(t-1) + take k_t, so
 // that the output's last column is n_t . q_t (the normaliser of a gated matrix memory).  State and output rows then hold
-// vdim + 1 columns a head.  q is multiplied by q_scale in either form.
-template <typename TD, int PARTS, bool OUTPUTS, bool GATED>
+// vdim + 1 columns a head (norm_col; without it the state has vdim columns, as for a state-space scan whose decay and
+// step size are numbers per token and head).  q is multiplied by q_scale in every form.
+//
+// MODE 2: the decay is a vector per token and head, one factor per row of the state (per key channel),
+//     S_t = diag(keep[t, h, :]) S_(t-1) + k_t v_t^T,      token_keep float32 [tokens, heads * dim].
+//
+// qk_share: this many neighbouring heads read the same q and k columns (head h reads q at q_off + (h / qk_share) * dim):
+// the groups of a state-space scan, whose B and C are shared by the heads of a group.  1: a q and a k per head.
+constexpr int MODE_PLAIN = 0, MODE_GATED = 1, MODE_VECTOR = 2;
+template <typename TD, int PARTS, bool OUTPUTS, int MODE>
 __global__ void __launch_bounds__(LA_THREADS, 4)     // four blocks an SM (measured faster than three blocks without the few spills)
 linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long long partial_stride, long long ld,
                              int q_off, int k_off, int v_off, const float* __restrict__ decay,
@@ -52,7 +60,9 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
                              const int* __restrict__ segment_slot, float* __restrict__ out, int heads, int dim,
                              int vdim, int act, int num_slots, int num_segments, int chunk_rows, int phase,
                              float* __restrict__ chunk_state, const float* __restrict__ token_keep,
-                             const float* __restrict__ token_take, float q_scale) {
+                             const float* __restrict__ token_take, float q_scale, int norm_col, int qk_share) {
+  constexpr bool GATED = MODE == MODE_GATED;
+  constexpr bool VECTOR = MODE == MODE_VECTOR;
   constexpr int CW = 32 / PARTS;
   constexpr int CB = 4 * CW;
   constexpr int PADDED = LA_DPT + 4;                // a part's 32 values, 16-byte aligned and four banks apart from the next part's
@@ -61,9 +71,11 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
   constexpr int QK_LOADS = LA_TT * PARTS * LA_DPT / LA_THREADS;   // values of q (and of k) a thread stages per tile
   constexpr int V_LOADS = (LA_TT * CB + LA_THREADS - 1) / LA_THREADS;
   __shared__ __align__(16) float q_s[LA_TT * QS], k_s[LA_TT * QS], v_s[LA_TT * CB];
+  __shared__ __align__(16) float a_s[VECTOR ? LA_TT * QS : 4];
   __shared__ float keep_s[LA_TT];
   __shared__ int item[3];
-  const int vs = GATED ? vdim + 1 : vdim;     // columns of a head's state and of its output
+  const int vs = vdim + (GATED && norm_col ? 1 : 0);     // columns of a head's state and of its output
+  const int hq = (int)blockIdx.y / qk_share;
   pdl_launch_dependents();
   pdl_wait();
   const int h = blockIdx.y, col0 = blockIdx.z * CB;
@@ -94,7 +106,7 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
   if (row1 <= row0) return;
   const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
   const int part = lane / CW, cb = warp * CW + lane % CW, col = col0 + cb;
-  const float decay_h = GATED ? 1.f : decay[h];
+  const float decay_h = MODE == MODE_PLAIN ? decay[h] : 1.f;
   float* st = chunk_rows == 0
       ? state + ((size_t)LSE_CHECKED(segment_slot[seg], 0, num_slots, 0, LSE_CHECK_ROW) * heads + h) * dim * vs
       : chunk_state + ((size_t)blockIdx.x * heads + h) * dim * vs;
@@ -106,7 +118,7 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
     const int d = part * LA_DPT + i;
     s[i] = (!from_zero && d < dim && col < vs) ? st[(size_t)d * vs + col] : 0.f;
   }
-  float qv[QK_LOADS], kv[QK_LOADS], vv_in[V_LOADS], take[QK_LOADS];
+  float qv[QK_LOADS], kv[QK_LOADS], vv_in[V_LOADS], take[QK_LOADS], av[VECTOR ? QK_LOADS : 1];
   auto fetch = [&](int base) {      // a tile's q, k and v into registers, all loads in flight together
     const int n = min(LA_TT, row1 - base);
 #pragma unroll
@@ -114,11 +126,13 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
       const int e = threadIdx.x + i * LA_THREADS;
       const int t = e / (PARTS * LA_DPT), d = e % (PARTS * LA_DPT);
       qv[i] = kv[i] = take[i] = 0.f;
+      if (VECTOR) av[i] = 0.f;
       if (t < n && d < dim) {
-        const TD* row = proj + (size_t)(base + t) * ld + h * dim + d;
+        const TD* row = proj + (size_t)(base + t) * ld + hq * dim + d;
         qv[i] = la_load(row + q_off, n_partials, partial_stride);
         kv[i] = la_load(row + k_off, n_partials, partial_stride);
         if (GATED) take[i] = token_take[(size_t)(base + t) * heads + h];
+        if (VECTOR) av[i] = token_keep[((size_t)(base + t) * heads + h) * dim + d];
       }
     }
 #pragma unroll
@@ -128,7 +142,7 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
       vv_in[i] = 0.f;
       if (e < LA_TT * CB && t < n && col0 + c < vdim)
         vv_in[i] = la_load(proj + (size_t)(base + t) * ld + v_off + h * vdim + col0 + c, n_partials, partial_stride);
-      else if (GATED && e < LA_TT * CB && t < n && col0 + c == vdim)
+      else if (GATED && norm_col && e < LA_TT * CB && t < n && col0 + c == vdim)
         vv_in[i] = 1.f;      // the normaliser's column
     }
   };
@@ -143,29 +157,32 @@ linear_attention_scan_kernel(const TD* __restrict__ proj, int n_partials, long l
       const int at = t * QS + (d / LA_DPT) * PADDED + d % LA_DPT;
       q_s[at] = la_act(qv[i], act) * q_scale;
       k_s[at] = GATED ? la_act(kv[i], act) * take[i] : la_act(kv[i], act);
+      if (VECTOR) a_s[at] = av[i];
     }
     if (GATED && threadIdx.x < LA_TT)
       keep_s[threadIdx.x] = (int)threadIdx.x < n ? token_keep[(size_t)(base + threadIdx.x) * heads + h] : 1.f;
 #pragma unroll
     for (int i = 0; i < V_LOADS; ++i) {
       const int e = threadIdx.x + i * LA_THREADS;
-      if (e < LA_TT * CB) v_s[e] = (GATED && col0 + e % CB == vdim) ? vv_in[i] : la_act(vv_in[i], act);
+      if (e < LA_TT * CB) v_s[e] = (GATED && norm_col && col0 + e % CB == vdim) ? vv_in[i] : la_act(vv_in[i], act);
     }
     __syncthreads();
     if (base + LA_TT < row1) fetch(base + LA_TT);    // the next tile travels while this one is worked on
     for (int t = 0; t < n; ++t) {
       const float4* qr = reinterpret_cast<const float4*>(q_s + t * QS + part * PADDED);
       const float4* kr = reinterpret_cast<const float4*>(k_s + t * QS + part * PADDED);
+      const float4* ar = reinterpret_cast<const float4*>(a_s + (VECTOR ? t * QS + part * PADDED : 0));
       const float vv = v_s[t * CB + cb];
       const float dk = GATED ? keep_s[t] : decay_h;
       float o[4] = {0.f, 0.f, 0.f, 0.f};     // four short chains instead of one of 32 dependent additions
 #pragma unroll
       for (int i = 0; i < LA_DPT / 4; ++i) {
         const float4 kq = kr[i], qq = OUTPUTS ? qr[i] : make_float4(0.f, 0.f, 0.f, 0.f);
-        s[4 * i + 0] = fmaf(dk, s[4 * i + 0], kq.x * vv);
-        s[4 * i + 1] = fmaf(dk, s[4 * i + 1], kq.y * vv);
-        s[4 * i + 2] = fmaf(dk, s[4 * i + 2], kq.z * vv);
-        s[4 * i + 3] = fmaf(dk, s[4 * i + 3], kq.w * vv);
+        const float4 aa = VECTOR ? ar[i] : make_float4(dk, dk, dk, dk);
+        s[4 * i + 0] = fmaf(aa.x, s[4 * i + 0], kq.x * vv);
+        s[4 * i + 1] = fmaf(aa.y, s[4 * i + 1], kq.y * vv);
+        s[4 * i + 2] = fmaf(aa.z, s[4 * i + 2], kq.z * vv);
+        s[4 * i + 3] = fmaf(aa.w, s[4 * i + 3], kq.w * vv);
         if (OUTPUTS) {
           o[0] = fmaf(s[4 * i + 0], qq.x, o[0]); o[1] = fmaf(s[4 * i + 1], qq.y, o[1]);
           o[2] = fmaf(s[4 * i + 2], qq.z, o[2]); o[3] = fmaf(s[4 * i + 3], qq.w, o[3]);
@@ -281,6 +298,66 @@ linear_attention_gated_carry_kernel(const float* __restrict__ token_keep, float*
   *slot = running;
 }
 
+// The vector form's carry.  First every chunk's factors, one per row of the state: the product of its tokens' keep
+// vectors, chunk_keep[chunk][head][dim] (a block per chunk and head, a thread per row).
+__global__ void __launch_bounds__(256)
+linear_attention_chunk_keep_kernel(const float* __restrict__ token_keep, const int* __restrict__ segment_start,
+                                   float* __restrict__ chunk_keep, int heads, int dim, int num_segments, int chunk_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int h = blockIdx.y;
+  int before = 0, first = 0, last = 0;
+  bool found = false;
+  for (int s = 0; s < num_segments && !found; ++s) {
+    const int a = segment_start[s], b = segment_start[s + 1];
+    const int chunks = (b - a + chunk_rows - 1) / chunk_rows;
+    if ((int)blockIdx.x < before + chunks) {
+      found = true;
+      first = a + ((int)blockIdx.x - before) * chunk_rows;
+      last = min(b, first + chunk_rows);
+    }
+    before += chunks;
+  }
+  if (!found) return;
+  for (int d = threadIdx.x; d < dim; d += blockDim.x) {
+    float product = 1.f;
+    for (int r = first; r < last; ++r) product *= token_keep[((size_t)r * heads + h) * dim + d];
+    chunk_keep[((size_t)blockIdx.x * heads + h) * dim + d] = product;
+  }
+}
+
+// Then, as above, every element carried from chunk to chunk with its row's factor.
+__global__ void __launch_bounds__(256)
+linear_attention_vector_carry_kernel(const float* __restrict__ chunk_keep, float* __restrict__ state,
+                                     const int* __restrict__ segment_start, const int* __restrict__ segment_slot,
+                                     float* __restrict__ chunk_state, int heads, int dim, int vs, int num_slots,
+                                     int chunk_rows) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int seg = blockIdx.z, h = blockIdx.y;
+  const int a = segment_start[seg], b = segment_start[seg + 1];
+  if (b <= a) return;
+  const int chunks = (b - a + chunk_rows - 1) / chunk_rows;
+  const int per_head = dim * vs;
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= per_head) return;
+  const int d = e / vs;
+  int before = 0;
+  for (int s = 0; s < seg; ++s) before += (segment_start[s + 1] - segment_start[s] + chunk_rows - 1) / chunk_rows;
+  const size_t per_state = (size_t)heads * per_head;
+  const size_t at = (size_t)h * per_head + e;
+  float* slot = state + (size_t)LSE_CHECKED(segment_slot[seg], 0, num_slots, 0, LSE_CHECK_ROW) * per_state + at;
+  float running = *slot;
+  float* own = chunk_state + (size_t)before * per_state + at;
+  const float* factor = chunk_keep + ((size_t)before * heads + h) * dim + d;
+  for (int c = 0; c < chunks; ++c) {
+    const float mine = own[(size_t)c * per_state];
+    own[(size_t)c * per_state] = running;
+    running = fmaf(factor[(size_t)c * heads * dim], running, mine);
+  }
+  *slot = running;
+}
+
 // out[t] = o[t] / sqrt(mean(o[t]^2) + eps) * weight * sigmoid(g[t]); g: columns g_off .. g_off + n of proj.
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(256)
@@ -302,6 +379,83 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const TD* __restrict__ proj, i
     out[(size_t)t * n + i] = from_f32<TO>(((row[i] * inv) * weight[i]) * gate);
   }
 }
+// What a state-space scan with one decay per head takes from its step sizes: dt = softplus(z + bias_h) (no clamp),
+// keep = exp(-exp(a_log_h) dt), take = dt; z is column dt_off + h of proj.  A thread per (token, head).
+template <typename TD>
+__global__ void __launch_bounds__(256)
+ssd_gates_kernel(const TD* __restrict__ proj, int n_partials, long long partial_stride, long long ld, int dt_off,
+                 const float* __restrict__ dt_bias, const float* __restrict__ a_log, float* __restrict__ keep,
+                 float* __restrict__ take, int tokens, int heads) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int e = blockIdx.x * blockDim.x + threadIdx.x;
+  if (e >= tokens * heads) return;
+  const int t = e / heads, h = e % heads;
+  const float z = la_load(proj + (size_t)t * ld + dt_off + h, n_partials, partial_stride) + dt_bias[h];
+  const float dt = fmaxf(z, 0.f) + log1pf(expf(-fabsf(z)));
+  keep[e] = expf(-expf(a_log[h]) * dt);
+  take[e] = dt;
+}
+
+// A decay per channel: keep = sigmoid(z + bias)^(1 / tau) = exp(log sigmoid(z + bias) / tau); z is column off + i of proj.
+template <typename TD>
+__global__ void __launch_bounds__(256)
+sigmoid_power_kernel(const TD* __restrict__ proj, int n_partials, long long partial_stride, long long ld, int off,
+                     const float* __restrict__ bias, float inv_tau, float* __restrict__ keep, int tokens, int n) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long e = blockIdx.x * (long long)blockDim.x + threadIdx.x;
+  if (e >= (long long)tokens * n) return;
+  const int t = (int)(e / n), i = (int)(e % n);
+  float z = la_load(proj + (size_t)t * ld + off + i, n_partials, partial_stride);
+  if (bias) z += bias[i];
+  const float log_sigmoid = fminf(z, 0.f) - log1pf(expf(-fabsf(z)));
+  keep[e] = expf(log_sigmoid * inv_tau);
+}
+
+// The norm behind a scan, in `groups` equal parts of a row, each by its own root mean square:
+//   a_i = o_i + skip[i / head_width] * x_i          (skip null: a = o;  x: columns x_off .. of `xsrc`)
+//   gate_first:  b = a * act(g);  out = b / rms(b) * weight[i % weight_len] * scale
+//   else:                         out = a / rms(a) * weight[i % weight_len] * act(g) * scale
+// with act the SiLU (gate_act 1) or the sigmoid (0); g: columns g_off .. of proj.  A warp owns a part at a time.
+template <typename TD, typename TO>
+__global__ void __launch_bounds__(256)
+gated_group_rmsnorm_kernel(const float* __restrict__ o, const TD* __restrict__ proj, int n_partials,
+                           long long partial_stride, long long ld, int g_off, const TO* __restrict__ xsrc,
+                           long long x_ld, int x_off, const float* __restrict__ skip, int head_width,
+                           const float* __restrict__ weight, int weight_len, TO* __restrict__ out, long long out_ld,
+                           int n, int groups, float eps, float scale, int gate_first, int gate_act,
+                           const int* __restrict__ segment_of_token) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const int t = blockIdx.x;
+  if (segment_of_token && segment_of_token[t] < 0) return;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
+  const int width = n / groups;
+  const float* row = o + (size_t)t * n;
+  const TD* g = proj + (size_t)t * ld + g_off;
+  auto gate = [&](int i) {
+    const float z = la_load(g + i, n_partials, partial_stride);
+    const float sg = 1.f / (1.f + expf(-z));
+    return gate_act == 1 ? z * sg : sg;
+  };
+  auto value = [&](int i) {
+    float a = row[i];
+    if (skip) a = fmaf(skip[i / head_width], to_f32<TO>(xsrc[(size_t)t * x_ld + x_off + i]), a);
+    return gate_first ? a * gate(i) : a;
+  };
+  for (int part = warp; part < groups; part += warps) {
+    const int lo = part * width;
+    float sq = 0.f;
+    for (int i = lo + lane; i < lo + width; i += 32) { const float v = value(i); sq = fmaf(v, v, sq); }
+    const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+    for (int i = lo + lane; i < lo + width; i += 32) {
+      float y = (value(i) * inv) * weight[i % weight_len];
+      if (!gate_first) y *= gate(i);
+      out[(size_t)t * out_ld + i] = from_f32<TO>(y * scale);
+    }
+  }
+}
 }  // namespace
 
 // chunk_rows == 0: one block row per request of the step (max_segments), empty requests leave at once.
@@ -309,17 +463,20 @@ gated_rmsnorm_kernel(const float* __restrict__ o, const TD* __restrict__ proj, i
 // [heads][dim][columns] (max_chunks >= tokens / chunk_rows + max_segments bounds the number of chunks).
 // token_keep, token_take (float32 [tokens, heads], or both null): the gated form, whose states and outputs have
 // vdim + 1 columns a head; decay is not read then.
-template <bool GATED>
+template <int MODE>
 static int linear_attention_scan_launch(const void* proj, int proj_dtype, int n_partials, long long partial_stride,
                                         long long ld, int q_off, int k_off, int v_off, const float* decay,
                                         float* state, const int* segment_start, const int* segment_slot, float* out,
                                         int max_segments, int heads, int dim, int vdim, int act, int num_slots,
                                         int chunk_rows, float* chunk_state, int max_chunks, const float* token_keep,
-                                        const float* token_take, float q_scale, cudaStream_t stream) {
+                                        const float* token_take, float q_scale, int norm_col, int qk_share,
+                                        float* chunk_keep, cudaStream_t stream) {
   if (max_segments <= 0) return 0;
   if (heads <= 0 || dim <= 0 || vdim <= 0 || dim > 8 * LA_DPT || heads > 65535) return LSE_ERR_BAD_ARGUMENT;
+  if (qk_share <= 0 || heads % qk_share) return LSE_ERR_BAD_ARGUMENT;
   if (chunk_rows < 0 || (chunk_rows > 0 && (chunk_state == nullptr || max_chunks <= 0))) return LSE_ERR_BAD_ARGUMENT;
-  const int vs = GATED ? vdim + 1 : vdim;
+  if (MODE == MODE_VECTOR && chunk_rows > 0 && chunk_keep == nullptr) return LSE_ERR_BAD_ARGUMENT;
+  const int vs = vdim + (MODE == MODE_GATED && norm_col ? 1 : 0);
   int parts = 1;
   while (parts * LA_DPT < dim) parts <<= 1;
 #define LSE_LA_CASE(TD, P)                                                                                       \
@@ -328,23 +485,30 @@ static int linear_attention_scan_launch(const void* proj, int proj_dtype, int n_
     dim3 grid(chunk_rows ? max_chunks : max_segments, heads, (vs + cb - 1) / cb);                                \
     for (int phase = 1; phase <= (chunk_rows ? 2 : 1); ++phase) {                                                \
       if (chunk_rows && phase == 1)                                                                              \
-        lse_launch(linear_attention_scan_kernel<TD, P, false, GATED>, grid, LA_THREADS, 0, stream,               \
+        lse_launch(linear_attention_scan_kernel<TD, P, false, MODE>, grid, LA_THREADS, 0, stream,                \
                    (const TD*)proj, n_partials, partial_stride, ld, q_off, k_off, v_off, decay, state,           \
                    segment_start, segment_slot, out, heads, dim, vdim, act, num_slots, max_segments, chunk_rows, \
-                   phase, chunk_state, token_keep, token_take, q_scale);                                         \
+                   phase, chunk_state, token_keep, token_take, q_scale, norm_col, qk_share);                     \
       else                                                                                                       \
-        lse_launch(linear_attention_scan_kernel<TD, P, true, GATED>, grid, LA_THREADS, 0, stream,                \
+        lse_launch(linear_attention_scan_kernel<TD, P, true, MODE>, grid, LA_THREADS, 0, stream,                 \
                    (const TD*)proj, n_partials, partial_stride, ld, q_off, k_off, v_off, decay, state,           \
                    segment_start, segment_slot, out, heads, dim, vdim, act, num_slots, max_segments, chunk_rows, \
-                   phase, chunk_state, token_keep, token_take, q_scale);                                         \
+                   phase, chunk_state, token_keep, token_take, q_scale, norm_col, qk_share);                     \
       if (chunk_rows && phase == 1) {                                                                            \
         const size_t per_state = (size_t)heads * dim * vs;                                                       \
-        if (GATED)                                                                                               \
+        if (MODE == MODE_GATED)                                                                                  \
           lse_launch(linear_attention_gated_carry_kernel, dim3((unsigned)((dim * vs + 255) / 256), heads,        \
                                                                max_segments),                                   \
                      256, sizeof(float) * (size_t)max_chunks, stream, token_keep, state, segment_start,          \
                      segment_slot, chunk_state, heads, dim, vs, num_slots, chunk_rows);                          \
-        else                                                                                                     \
+        else if (MODE == MODE_VECTOR) {                                                                          \
+          lse_launch(linear_attention_chunk_keep_kernel, dim3(max_chunks, heads), dim >= 128 ? 128 : 64, 0,      \
+                     stream, token_keep, segment_start, chunk_keep, heads, dim, max_segments, chunk_rows);       \
+          lse_launch(linear_attention_vector_carry_kernel, dim3((unsigned)((dim * vs + 255) / 256), heads,       \
+                                                                max_segments),                                  \
+                     256, 0, stream, (const float*)chunk_keep, state, segment_start, segment_slot, chunk_state,  \
+                     heads, dim, vs, num_slots, chunk_rows);                                                     \
+        } else                                                                                                   \
           lse_launch(linear_attention_carry_kernel, dim3((unsigned)((per_state + 255) / 256), max_segments),     \
                      256, 0, stream, decay, state, segment_start, segment_slot, chunk_state, heads, dim, vdim,   \
                      num_slots, chunk_rows);                                                                     \
@@ -371,10 +535,27 @@ extern "C" int lse_linear_attention_scan(const void* proj, int proj_dtype, int n
                                          float* state, const int* segment_start, const int* segment_slot, float* out,
                                          int max_segments, int heads, int dim, int vdim, int act, int num_slots,
                                          int chunk_rows, float* chunk_state, int max_chunks, cudaStream_t stream) {
-  return linear_attention_scan_launch<false>(proj, proj_dtype, n_partials, partial_stride, ld, q_off, k_off, v_off,
-                                             decay, state, segment_start, segment_slot, out, max_segments, heads, dim,
-                                             vdim, act, num_slots, chunk_rows, chunk_state, max_chunks, nullptr,
-                                             nullptr, 1.0f, stream);
+  return linear_attention_scan_launch<MODE_PLAIN>(proj, proj_dtype, n_partials, partial_stride, ld, q_off, k_off, v_off,
+                                                  decay, state, segment_start, segment_slot, out, max_segments, heads,
+                                                  dim, vdim, act, num_slots, chunk_rows, chunk_state, max_chunks, nullptr,
+                                                  nullptr, 1.0f, 0, 1, nullptr, stream);
+}
+
+// norm_col: the state carries the normaliser's column (vdim + 1 columns); qk_share: heads that share a q and a k.
+extern "C" int lse_gated_linear_attention_scan_shared(const void* proj, int proj_dtype, int n_partials,
+                                                      long long partial_stride, long long ld, int q_off, int k_off,
+                                                      int v_off, const float* token_keep, const float* token_take,
+                                                      float q_scale, float* state, const int* segment_start,
+                                                      const int* segment_slot, float* out, int max_segments, int heads,
+                                                      int dim, int vdim, int num_slots, int chunk_rows,
+                                                      float* chunk_state, int max_chunks, int norm_col, int qk_share,
+                                                      cudaStream_t stream) {
+  if (!token_keep || !token_take) return LSE_ERR_BAD_ARGUMENT;
+  if (max_chunks > 12000) return LSE_ERR_TOO_LARGE;      // a chunk's factor lives in shared memory during the carry
+  return linear_attention_scan_launch<MODE_GATED>(proj, proj_dtype, n_partials, partial_stride, ld, q_off, k_off, v_off,
+                                                  nullptr, state, segment_start, segment_slot, out, max_segments, heads,
+                                                  dim, vdim, 0, num_slots, chunk_rows, chunk_state, max_chunks,
+                                                  token_keep, token_take, q_scale, norm_col, qk_share, nullptr, stream);
 }
 
 extern "C" int lse_gated_linear_attention_scan(const void* proj, int proj_dtype, int n_partials,
@@ -384,12 +565,25 @@ extern "C" int lse_gated_linear_attention_scan(const void* proj, int proj_dtype,
                                                float* out, int max_segments, int heads, int dim, int vdim,
                                                int num_slots, int chunk_rows, float* chunk_state, int max_chunks,
                                                cudaStream_t stream) {
-  if (!token_keep || !token_take) return LSE_ERR_BAD_ARGUMENT;
-  if (max_chunks > 12000) return LSE_ERR_TOO_LARGE;      // a chunk's factor lives in shared memory during the carry
-  return linear_attention_scan_launch<true>(proj, proj_dtype, n_partials, partial_stride, ld, q_off, k_off, v_off,
-                                            nullptr, state, segment_start, segment_slot, out, max_segments, heads, dim,
-                                            vdim, 0, num_slots, chunk_rows, chunk_state, max_chunks, token_keep,
-                                            token_take, q_scale, stream);
+  return lse_gated_linear_attention_scan_shared(proj, proj_dtype, n_partials, partial_stride, ld, q_off, k_off, v_off,
+                                                token_keep, token_take, q_scale, state, segment_start, segment_slot, out,
+                                                max_segments, heads, dim, vdim, num_slots, chunk_rows, chunk_state,
+                                                max_chunks, 1, 1, stream);
+}
+
+// The decay is a vector per token and head: token_keep float32 [tokens, heads * dim]; chunk_keep (chunked only) holds
+// max_chunks * heads * dim floats.
+extern "C" int lse_vector_decay_attention_scan(const void* proj, int proj_dtype, int n_partials, long long partial_stride,
+                                               long long ld, int q_off, int k_off, int v_off, const float* token_keep,
+                                               float q_scale, float* state, const int* segment_start,
+                                               const int* segment_slot, float* out, int max_segments, int heads, int dim,
+                                               int vdim, int num_slots, int chunk_rows, float* chunk_state,
+                                               int max_chunks, float* chunk_keep, cudaStream_t stream) {
+  if (!token_keep) return LSE_ERR_BAD_ARGUMENT;
+  return linear_attention_scan_launch<MODE_VECTOR>(proj, proj_dtype, n_partials, partial_stride, ld, q_off, k_off, v_off,
+                                                   nullptr, state, segment_start, segment_slot, out, max_segments, heads,
+                                                   dim, vdim, 0, num_slots, chunk_rows, chunk_state, max_chunks,
+                                                   token_keep, nullptr, q_scale, 0, 1, chunk_keep, stream);
 }
 
 extern "C" int lse_gated_rmsnorm(const float* o, const void* proj, int proj_dtype, int n_partials,
@@ -407,5 +601,67 @@ extern "C" int lse_gated_rmsnorm(const float* o, const void* proj, int proj_dtyp
   else if (!d32 && o32) LSE_GN_CASE(__nv_bfloat16, float)
   else LSE_GN_CASE(__nv_bfloat16, __nv_bfloat16)
 #undef LSE_GN_CASE
+  LSE_LAUNCH_CHECK();
+}
+
+// keep, take float32 [tokens, heads]; proj float32 / bfloat16 rows or a float32 stack of partial sums.
+extern "C" int lse_ssd_gates(const void* proj, int proj_dtype, int n_partials, long long partial_stride, long long ld,
+                             int dt_off, const float* dt_bias, const float* a_log, float* keep, float* take, int tokens,
+                             int heads, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (heads <= 0 || n_partials < 1) return LSE_ERR_BAD_ARGUMENT;
+  const unsigned blocks = (unsigned)(((long long)tokens * heads + 255) / 256);
+  if (proj_dtype == LSE_DTYPE_F32)
+    lse_launch(ssd_gates_kernel<float>, blocks, 256, 0, stream, (const float*)proj, n_partials, partial_stride, ld, dt_off,
+               dt_bias, a_log, keep, take, tokens, heads);
+  else if (proj_dtype == LSE_DTYPE_BF16)
+    lse_launch(ssd_gates_kernel<__nv_bfloat16>, blocks, 256, 0, stream, (const __nv_bfloat16*)proj, n_partials,
+               partial_stride, ld, dt_off, dt_bias, a_log, keep, take, tokens, heads);
+  else
+    return LSE_ERR_BAD_ARGUMENT;
+  LSE_LAUNCH_CHECK();
+}
+
+// keep float32 [tokens, n] = sigmoid(proj[:, off .. off + n] + bias)^(1 / tau); bias float32 [n] or null.
+extern "C" int lse_sigmoid_power(const void* proj, int proj_dtype, int n_partials, long long partial_stride, long long ld,
+                                 int off, const float* bias, float tau, float* keep, int tokens, int n,
+                                 cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (n <= 0 || n_partials < 1 || !(tau > 0.f)) return LSE_ERR_BAD_ARGUMENT;
+  const long long blocks = ((long long)tokens * n + 255) / 256;
+  if (blocks > 0x7fffffffLL) return LSE_ERR_TOO_LARGE;
+  if (proj_dtype == LSE_DTYPE_F32)
+    lse_launch(sigmoid_power_kernel<float>, (unsigned)blocks, 256, 0, stream, (const float*)proj, n_partials,
+               partial_stride, ld, off, bias, 1.0f / tau, keep, tokens, n);
+  else if (proj_dtype == LSE_DTYPE_BF16)
+    lse_launch(sigmoid_power_kernel<__nv_bfloat16>, (unsigned)blocks, 256, 0, stream, (const __nv_bfloat16*)proj,
+               n_partials, partial_stride, ld, off, bias, 1.0f / tau, keep, tokens, n);
+  else
+    return LSE_ERR_BAD_ARGUMENT;
+  LSE_LAUNCH_CHECK();
+}
+
+// o float32 [tokens, n]; the gate in proj (float32 / bfloat16 / partial sums); xsrc (the output's dtype, rows x_ld apart) and
+// skip float32 [n / head_width], or both null; weight float32 [weight_len], read at i % weight_len; out rows out_ld apart.
+extern "C" int lse_gated_group_rmsnorm(const float* o, const void* proj, int proj_dtype, int n_partials,
+                                       long long partial_stride, long long ld, int g_off, const void* xsrc, long long x_ld,
+                                       int x_off, const float* skip, int head_width, const float* weight, int weight_len,
+                                       void* out, int out_dtype, long long out_ld, int tokens, int n, int groups, float eps,
+                                       float scale, int gate_first, int gate_act, const int* segment_of_token,
+                                       cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (n <= 0 || groups <= 0 || n % groups || weight_len <= 0 || n_partials < 1 || (skip && (!xsrc || head_width <= 0)))
+    return LSE_ERR_BAD_ARGUMENT;
+  const int threads = groups >= 8 ? 256 : (groups >= 4 ? 128 : 32 * groups);
+#define LSE_GGN_CASE(TD, TO)                                                                                         \
+  lse_launch(gated_group_rmsnorm_kernel<TD, TO>, tokens, threads, 0, stream, o, (const TD*)proj, n_partials,          \
+             partial_stride, ld, g_off, (const TO*)xsrc, x_ld, x_off, skip, head_width, weight, weight_len, (TO*)out, \
+             out_ld, n, groups, eps, scale, gate_first, gate_act, segment_of_token);
+  const bool d32 = proj_dtype == LSE_DTYPE_F32, o32 = out_dtype == LSE_DTYPE_F32;
+  if (d32 && o32) LSE_GGN_CASE(float, float)
+  else if (d32 && !o32) LSE_GGN_CASE(float, __nv_bfloat16)
+  else if (!d32 && o32) LSE_GGN_CASE(__nv_bfloat16, float)
+  else LSE_GGN_CASE(__nv_bfloat16, __nv_bfloat16)
+#undef LSE_GGN_CASE
   LSE_LAUNCH_CHECK();
 }

@@ -98,6 +98,102 @@ moe_route_kernel(const float* __restrict__ logits, int n_partials, long long par
   if (lane == 0) identity_weight[t] = identity_sum;
 }
 
+// A router whose scores are sigmoids, chosen within the best groups of experts (a warp per token, float32):
+//   s_e = sigmoid(z_e);  c_e = s_e + correction_e  (the choice score);
+//   the experts form `group_count` equal groups of neighbours; a group's score is the sum of its two largest c (of its
+//   one c when a group is a single expert); only the `group_keep` best groups' experts can be chosen (group_count <= 1:
+//   all experts);  the `top` largest c among them are chosen (ties: the lower index);
+//   weight_e = s_e / (sum of the chosen s + 1e-20) * scale.
+// Leaves what moe_route_kernel leaves: the dense row of weights, the choices, a zero identity weight, the shared gate.
+__global__ void __launch_bounds__(ROUTE_THREADS)
+moe_route_sigmoid_kernel(const float* __restrict__ logits, int n_partials, long long partial_stride, int ld,
+                         const float* __restrict__ correction, int has_shared_gate, float* __restrict__ expert_weights,
+                         float* __restrict__ identity_weight, float* __restrict__ shared_gate, int* __restrict__ chosen_out,
+                         int tokens, int experts, int top, int group_count, int group_keep, float scale) {
+  extern __shared__ float smem[];   // per warp: [experts] scores, [experts] choice scores, [groups] group scores
+  pdl_launch_dependents();
+  pdl_wait();
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int t = blockIdx.x * (ROUTE_THREADS / 32) + warp;
+  if (t >= tokens) return;
+  const int groups = group_count > 1 ? group_count : 1;
+  float* score = smem + (size_t)warp * (2 * experts + groups);
+  float* choice = score + experts;
+  float* group_score = choice + experts;
+  const float* row = logits + (size_t)t * ld;
+  auto logit = [&](int e) {
+    float sum = 0.f;
+    for (int p = 0; p < n_partials; ++p) sum += row[(size_t)p * partial_stride + e];
+    return sum;
+  };
+  for (int e = lane; e < experts; e += 32) {
+    const float sg = 1.0f / (1.0f + expf(-logit(e)));
+    score[e] = sg;
+    choice[e] = correction ? sg + correction[e] : sg;
+    expert_weights[(size_t)t * experts + e] = 0.f;
+  }
+  if (has_shared_gate && lane == 0) shared_gate[t] = 1.0f / (1.0f + expf(-logit(experts)));
+  __syncwarp();
+  if (group_count > 1 && group_keep < group_count) {
+    const int per = experts / group_count;
+    for (int g = lane; g < group_count; g += 32) {
+      float first = -INFINITY, second = -INFINITY;
+      for (int e = g * per; e < (g + 1) * per; ++e) {
+        const float c = choice[e];
+        if (c > first) { second = first; first = c; }
+        else if (c > second) second = c;
+      }
+      group_score[g] = per > 1 ? first + second : first;
+    }
+    __syncwarp();
+    // a group is kept when fewer than group_keep groups come before it (a larger score, or an equal one at a lower index)
+    for (int g = lane; g < group_count; g += 32) {
+      const float mine = group_score[g];
+      int ahead = 0;
+      for (int o = 0; o < group_count; ++o) {
+        const float other = group_score[o];
+        ahead += (other > mine || (other == mine && o < g)) ? 1 : 0;
+      }
+      if (ahead >= group_keep)
+        for (int e = g * per; e < (g + 1) * per; ++e) choice[e] = -INFINITY;
+    }
+    __syncwarp();
+  }
+  float chosen_sum = 0.f;
+  int taken = 0;
+  for (int k = 0; k < top; ++k) {
+    float best = -INFINITY;
+    int best_e = 0x7fffffff;
+    for (int e = lane; e < experts; e += 32) {
+      const float c = choice[e];
+      if (c > best) { best = c; best_e = e; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+      const float other = __shfl_xor_sync(0xffffffffu, best, o);
+      const int other_e = __shfl_xor_sync(0xffffffffu, best_e, o);
+      if (other > best || (other == best && other_e < best_e)) { best = other; best_e = other_e; }
+    }
+    if (best_e >= experts) {   // nothing left to choose from
+      if (chosen_out && lane == 0)
+        for (int rest = k; rest < top; ++rest) chosen_out[(size_t)t * top + rest] = -1;
+      break;
+    }
+    chosen_sum += score[best_e];
+    ++taken;
+    if (lane == 0) {
+      choice[best_e] = -INFINITY;
+      expert_weights[(size_t)t * experts + best_e] = score[best_e];
+      if (chosen_out) chosen_out[(size_t)t * top + k] = best_e;
+    }
+    __syncwarp();
+  }
+  const float factor = scale / (chosen_sum + 1e-20f);
+  for (int e = lane; e < experts; e += 32) expert_weights[(size_t)t * experts + e] *= factor;
+  if (lane == 0) identity_weight[t] = 0.f;
+  (void)taken;
+}
+
 template <typename T> __device__ __forceinline__ void moe_load8(const T* p, float (&v)[8]);
 template <> __device__ __forceinline__ void moe_load8<float>(const float* p, float (&v)[8]) {
   const float4 a = *reinterpret_cast<const float4*>(p), b = *reinterpret_cast<const float4*>(p + 4);
@@ -143,6 +239,22 @@ __global__ void moe_gated_act8_kernel(const TI* __restrict__ gate_up, int n_part
   if (c == 0.f) {
 #pragma unroll
     for (int e = 0; e < 8; ++e) y[e] = 0.f;
+    moe_store8<TO>(dst, y);
+    return;
+  }
+  if (kind == 2) {      // experts without a gate: the row holds one column per output, out = c * relu(u)^2
+    const TI* row = gate_up + (size_t)t * inter + i;
+    float u[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) u[e] = 0.f;
+    for (int p = 0; p < n_partials; ++p) {
+      float b[8];
+      moe_load8<TI>(row + (size_t)p * partial_stride, b);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) u[e] += b[e];
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) { const float r = fmaxf(u[e], 0.f); y[e] = c * (r * r); }
     moe_store8<TO>(dst, y);
     return;
   }
@@ -195,6 +307,13 @@ __global__ void moe_gated_act_kernel(const TI* __restrict__ gate_up, int n_parti
                          : (expert_weights ? expert_weights[(size_t)t * experts + i / ff] : 1.f);
   TO* dst = out + (size_t)t * inter + i;
   if (c == 0.f) { *dst = from_f32<TO>(0.f); return; }   // an expert that the token did not choose
+  if (kind == 2) {
+    float u = 0.f;
+    for (int p = 0; p < n_partials; ++p) u += to_f32<TI>(gate_up[(size_t)p * partial_stride + (size_t)t * inter + i]);
+    u = fmaxf(u, 0.f);
+    *dst = from_f32<TO>(c * (u * u));
+    return;
+  }
   const TI* row = gate_up + (size_t)t * 2 * inter;
   const int gate_at = shared ? 2 * experts * ff + (i - experts * ff) : (i / ff) * 2 * ff + i % ff;
   const int up_at = gate_at + (shared ? shared_ff : ff);
@@ -343,6 +462,23 @@ extern "C" int lse_moe_route_biased(const float* logits, int n_partials, long lo
   LSE_LAUNCH_CHECK();
 }
 
+// As lse_moe_route, for sigmoid scores chosen within the best groups (see moe_route_sigmoid_kernel); no identity experts.
+extern "C" int lse_moe_route_sigmoid(const float* logits, int n_partials, long long partial_stride, int ld,
+                                     const float* correction, int has_shared_gate, float* expert_weights,
+                                     float* identity_weight, float* shared_gate, int* chosen, int tokens, int experts,
+                                     int top, int group_count, int group_keep, float scale, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (experts <= 0 || top <= 0 || n_partials < 1 || ld < experts + (has_shared_gate ? 1 : 0)) return LSE_ERR_BAD_ARGUMENT;
+  if (group_count > 1 && (experts % group_count || group_keep <= 0)) return LSE_ERR_BAD_ARGUMENT;
+  if (experts > 1024) return LSE_ERR_TOO_LARGE;
+  const int warps = ROUTE_THREADS / 32;
+  const size_t smem = sizeof(float) * (2 * (size_t)experts + (group_count > 1 ? group_count : 1)) * warps;
+  lse_launch(moe_route_sigmoid_kernel, (tokens + warps - 1) / warps, ROUTE_THREADS, smem, stream, logits, n_partials,
+             partial_stride, ld, correction, has_shared_gate, expert_weights, identity_weight, shared_gate, chosen, tokens,
+             experts, top, group_count, group_keep, scale);
+  LSE_LAUNCH_CHECK();
+}
+
 extern "C" int lse_moe_gated_act_kind(const void* gate_up, int in_dtype, int n_partials, long long partial_stride,
                                       const float* expert_weights, const float* shared_gate, void* out, int out_dtype,
                                       int tokens, int experts, int ff, int shared_ff, float limit, float shared_limit,
@@ -357,7 +493,8 @@ extern "C" int lse_moe_gated_act(const void* gate_up, int in_dtype, int n_partia
 }
 
 // kind 0: out = c * g' sigmoid(1.702 g') (u' + 1) with g' = min(g, limit), u' = clamp(u, -limit, limit);
-// kind 1: out = c * silu(g) * u.
+// kind 1: out = c * silu(g) * u;
+// kind 2: experts without a gate, the input row holds one column per output column: out = c * relu(u)^2.
 extern "C" int lse_moe_gated_act_kind(const void* gate_up, int in_dtype, int n_partials, long long partial_stride,
                                       const float* expert_weights, const float* shared_gate, void* out, int out_dtype,
                                       int tokens, int experts, int ff, int shared_ff, float limit, float shared_limit,

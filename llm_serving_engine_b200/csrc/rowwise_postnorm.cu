@@ -284,6 +284,76 @@ __global__ void head_norm_kv_write_kernel(const TI* __restrict__ proj, int n_par
   }
 }
 
+// The same with a rotation behind the norm: the first rot_dims values of every query and key head are rotated in pairs
+// (value i with value i + rot_dims / 2) by the angle position * freq[i], formed in double precision; cosine and sine are
+// multiplied by rot_factor.  A warp owns a head of a token and passes its normed values through shared memory, so
+// that a lane finds its partner's; heads up to 256 wide.
+template <typename TI, typename TO>
+__global__ void __launch_bounds__(128)
+head_norm_rope_kv_write_kernel(const TI* __restrict__ proj, int n_partials, long long partial_stride, long long ld,
+                               const float* __restrict__ bias, const float* __restrict__ q_norm,
+                               const float* __restrict__ k_norm, float eps, const int* __restrict__ slot_mapping,
+                               const int* __restrict__ positions, const double* __restrict__ freq, float rot_factor,
+                               int rot_dims, TO* __restrict__ q_out, TO* __restrict__ k_cache, TO* __restrict__ v_cache,
+                               int tokens, int n_q, int n_kv, int dk, int dv, int page_size, int num_pages) {
+  __shared__ float staged[4][256];
+  pdl_launch_dependents();
+  pdl_wait();
+  const int items = n_q + 2 * n_kv;
+  const int warp = (int)((blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5), lane = threadIdx.x & 31;
+  if (warp >= tokens * items) return;
+  const int t = warp / items, item = warp % items;
+  int column, width;
+  const float* norm_w = nullptr;
+  TO* dst = nullptr;
+  bool rotated = true;
+  const int slot = LSE_CHECKED(slot_mapping[t], -1, num_pages * page_size, -1, LSE_CHECK_CACHE_SLOT);
+  if (slot < 0) return;   // padding row
+  if (item < n_q) {
+    column = item * dk; width = dk; norm_w = q_norm;
+    dst = q_out + ((size_t)t * n_q + item) * dk;
+  } else {
+    const int page = slot / page_size, offset = slot % page_size;
+    if (item < n_q + n_kv) {
+      const int h = item - n_q;
+      column = n_q * dk + h * dk; width = dk; norm_w = k_norm;
+      dst = k_cache + (((size_t)page * n_kv + h) * page_size + offset) * dk;
+    } else {
+      const int h = item - n_q - n_kv;
+      column = (n_q + n_kv) * dk + h * dv; width = dv;
+      dst = v_cache + (((size_t)page * n_kv + h) * page_size + offset) * dv;
+      rotated = false;
+    }
+  }
+  const TI* src = proj + (size_t)t * ld + column;
+  float* mine = staged[threadIdx.x >> 5];
+  float sq = 0.f;
+  for (int i = lane; i < width; i += 32) {
+    float sum = 0.f;
+    for (int p = 0; p < n_partials; ++p) sum += to_f32<TI>(src[(size_t)p * partial_stride + i]);
+    if (bias) sum += bias[column + i];
+    mine[i] = sum;
+    sq = fmaf(sum, sum, sq);
+  }
+  const float inv = norm_w ? 1.0f / sqrtf(warp_sum(sq) / (float)width + eps) : 1.f;
+  __syncwarp();
+  const int half = rot_dims / 2;
+  const int position = positions[t];
+  for (int i = lane; i < width; i += 32) {
+    float x = norm_w ? (mine[i] * inv) * norm_w[i] : mine[i];
+    if (rotated && i < rot_dims) {
+      const int pair = i < half ? i : i - half;
+      const int other = i < half ? i + half : i - half;
+      const float y = norm_w ? (mine[other] * inv) * norm_w[other] : mine[other];
+      double sine, cosine;
+      sincos((double)position * freq[pair], &sine, &cosine);
+      const float c = (float)cosine * rot_factor, s = (float)sine * rot_factor;
+      x = i < half ? x * c - y * s : x * c + y * s;
+    }
+    dst[i] = from_f32<TO>(x);
+  }
+}
+
 __global__ void softcap_kernel(float* __restrict__ values, long long count, float cap) {
   pdl_launch_dependents();
   pdl_wait();
@@ -360,6 +430,34 @@ extern "C" int lse_head_norm_kv_write(const void* proj, int in_dtype, int n_part
   else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_HEADNORM_CASE(float, __nv_bfloat16);
   else return LSE_ERR_BAD_ARGUMENT;
 #undef LSE_HEADNORM_CASE
+  LSE_LAUNCH_CHECK();
+}
+
+// As lse_head_norm_kv_write, then the first rot_dims values of every query and key head rotated (freq float64
+// [rot_dims / 2], positions int32 [tokens], cosine and sine times rot_factor).  Heads up to 256 wide.
+extern "C" int lse_head_norm_rope_kv_write(const void* proj, int in_dtype, int n_partials, long long partial_stride,
+                                           long long ld, const float* bias, const float* q_norm, const float* k_norm,
+                                           float eps, const int* slot_mapping, const int* positions, const double* freq,
+                                           float rot_factor, int rot_dims, void* q_out, void* k_cache, void* v_cache,
+                                           int out_dtype, int tokens, int n_q, int n_kv, int dk, int dv, int page_size,
+                                           int num_pages, cudaStream_t stream) {
+  if (tokens <= 0) return 0;
+  if (n_q <= 0 || n_kv <= 0 || dk <= 0 || dv <= 0 || n_partials < 1 || dk > 256 || dv > 256) return LSE_ERR_BAD_ARGUMENT;
+  if (rot_dims < 0 || rot_dims % 2 || rot_dims > dk || (rot_dims > 0 && (!freq || !positions))) return LSE_ERR_BAD_ARGUMENT;
+  if (!k_cache || !v_cache || !slot_mapping || page_size <= 0) return LSE_ERR_BAD_ARGUMENT;
+  const long long warps = (long long)tokens * (n_q + 2 * n_kv);
+  const int threads = 128;
+  const long long blocks = (warps * 32 + threads - 1) / threads;
+  if (blocks > 0x7fffffffLL) return LSE_ERR_TOO_LARGE;
+#define LSE_HEADROPE_CASE(TI, TO)                                                                                      \
+  lse_launch(head_norm_rope_kv_write_kernel<TI, TO>, (unsigned)blocks, threads, 0, stream, (const TI*)proj, n_partials, \
+             partial_stride, ld, bias, q_norm, k_norm, eps, slot_mapping, positions, freq, rot_factor, rot_dims,       \
+             (TO*)q_out, (TO*)k_cache, (TO*)v_cache, tokens, n_q, n_kv, dk, dv, page_size, num_pages)
+  if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_F32) LSE_HEADROPE_CASE(float, float);
+  else if (in_dtype == LSE_DTYPE_BF16 && out_dtype == LSE_DTYPE_BF16) LSE_HEADROPE_CASE(__nv_bfloat16, __nv_bfloat16);
+  else if (in_dtype == LSE_DTYPE_F32 && out_dtype == LSE_DTYPE_BF16) LSE_HEADROPE_CASE(float, __nv_bfloat16);
+  else return LSE_ERR_BAD_ARGUMENT;
+#undef LSE_HEADROPE_CASE
   LSE_LAUNCH_CHECK();
 }
 

@@ -137,6 +137,28 @@ _SIGNATURES = {
                              c_int, c_int, c_int, c_int, c_void_p, c_int, c_void_p],
     "lse_moe_gated_act_kind": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                c_int, c_int, c_float, c_float, c_void_p, c_int, c_void_p],
+    "lse_gated_act_mul_limit": [c_void_p, c_int, c_int, c_longlong, c_void_p, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "lse_head_norm_rope_kv_write": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_void_p, c_void_p, c_void_p, c_float,
+                                    c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p, c_int,
+                                    c_int, c_int, c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "lse_attention_scored_windowed": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_void_p, c_int, c_void_p,
+                                      c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int,
+                                      c_int, c_float, c_int, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p],
+    "lse_gated_linear_attention_scan_shared": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int,
+                                               c_void_p, c_void_p, c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int,
+                                               c_int, c_int, c_int, c_int, c_int, c_void_p, c_int, c_int, c_int, c_void_p],
+    "lse_vector_decay_attention_scan": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_int, c_int, c_void_p,
+                                        c_float, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int,
+                                        c_int, c_void_p, c_int, c_void_p, c_void_p],
+    "lse_ssd_gates": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                      c_int, c_int, c_void_p],
+    "lse_sigmoid_power": [c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_float, c_void_p, c_int, c_int,
+                          c_void_p],
+    "lse_gated_group_rmsnorm": [c_void_p, c_void_p, c_int, c_int, c_longlong, c_longlong, c_int, c_void_p, c_longlong,
+                                c_int, c_void_p, c_int, c_void_p, c_int, c_void_p, c_int, c_longlong, c_int, c_int, c_int,
+                                c_float, c_float, c_int, c_int, c_void_p, c_void_p],
+    "lse_moe_route_sigmoid": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                              c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
     "lse_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "lse_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p],

@@ -387,20 +387,21 @@ def attention_tc_status() -> int:
     return int(library.load().lse_attention_tc_status())
 
 
-GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu": 2}
+GATE_ACTIVATIONS = {"silu": 0, "gelu_tanh": 1, "relu": 2, "clamped_swish": 3}
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu") -> torch.Tensor:
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, activation: str = "silu", limit: float = 0.0) -> torch.Tensor:
     """out[t, i] = act(gate_i) * up_i; ``gate_up`` is [T, 2I] (the row is [gate (I) | up (I)]) or a
-    float32 stack of partial sums [P, T, 2I]; ``activation``: "silu", "gelu_tanh" (the tanh form of GELU) or "relu"."""
+    float32 stack of partial sums [P, T, 2I]; ``activation``: "silu", "gelu_tanh" (the tanh form of GELU), "relu", or
+    "clamped_swish": g = min(gate, limit), u = clamp(up, -limit, limit), out = g sigmoid(1.702 g) (u + 1)."""
     _need_cuda(gate_up, out)
     tokens, two_i = gate_up.shape[-2], gate_up.shape[-1]
     assert two_i % 2 == 0 and out.shape == (tokens, two_i // 2) and out.is_contiguous()
     gate_up, n_partials, stride = _partials(gate_up, tokens, two_i)
     lib = library.load()
-    check(lib.lse_gated_act_mul(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride, out.data_ptr(),
-                                dtype_code(out.dtype), tokens, two_i // 2, GATE_ACTIVATIONS[activation], _stream()),
-          "silu_mul")
+    check(lib.lse_gated_act_mul_limit(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride, out.data_ptr(),
+                                      dtype_code(out.dtype), tokens, two_i // 2, GATE_ACTIVATIONS[activation],
+                                      float(limit), _stream()), "silu_mul")
     return out
 
 
@@ -808,20 +809,51 @@ def head_norm_kv_write(proj: torch.Tensor, bias: torch.Tensor | None, q_norm: to
                                                 _stream()), "head_norm_kv_write")
 
 
+def head_norm_rope_kv_write(proj: torch.Tensor, bias: torch.Tensor | None, q_norm: torch.Tensor | None,
+                            k_norm: torch.Tensor | None, eps: float, slot_mapping: torch.Tensor, positions: torch.Tensor,
+                            freq: torch.Tensor, rot_factor: float, q_out: torch.Tensor, k_cache: torch.Tensor,
+                            v_cache: torch.Tensor, n_q: int, n_kv: int, dk: int, dv: int, offset: int = 0) -> None:
+    """As :func:`head_norm_kv_write` (the row [q | k | v] starts at column ``offset`` of ``proj``; ``bias`` counts from
+    there), and behind the norm the first ``2 * len(freq)`` values of every query and key head
+    are rotated: value i with value i + len(freq), by the angle position * freq[i] (``freq`` float64, the angle formed
+    in double precision); cosine and sine are multiplied by ``rot_factor``.  Heads up to 256 wide."""
+    _need_cuda(proj, bias, q_norm, k_norm, slot_mapping, positions, freq, q_out, k_cache, v_cache)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = proj.shape[-2]
+    assert q_out.shape == (tokens, n_q, dk) and q_out.is_contiguous()
+    assert bias is None or bias.dtype == torch.float32
+    for weight in (q_norm, k_norm):
+        assert weight is None or (weight.dtype == torch.float32 and weight.shape == (dk,))
+    assert freq.dtype == torch.float64 and freq.is_contiguous() and positions.dtype == torch.int32
+    assert k_cache.is_contiguous() and v_cache.is_contiguous() and k_cache.dtype == v_cache.dtype == q_out.dtype
+    assert k_cache.shape[1] == n_kv and k_cache.shape[3] == dk and v_cache.shape[3] == dv
+    assert slot_mapping.dtype == torch.int32 and slot_mapping.shape[0] >= tokens
+    check(library.load().lse_head_norm_rope_kv_write(
+        proj.data_ptr() + int(offset) * proj.element_size(), code, n_partials, stride, ld, _ptr(bias), _ptr(q_norm), _ptr(k_norm), float(eps),
+        slot_mapping.data_ptr(), positions.data_ptr(), freq.data_ptr() if freq.numel() else None, float(rot_factor),
+        2 * freq.numel(), q_out.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), dtype_code(q_out.dtype), tokens, n_q,
+        n_kv, dk, dv, k_cache.shape[2], k_cache.shape[0], _stream()), "head_norm_rope_kv_write")
+
+
 def attention_scored(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
                      block_tables: torch.Tensor, segment_of_token: torch.Tensor, positions: torch.Tensor, scale: float,
                      r1: torch.Tensor | None = None, r2: torch.Tensor | None = None, sink: torch.Tensor | None = None,
                      cross: bool = False, split: bool | None = None, segment_start: torch.Tensor | None = None,
-                     segment_first_position: torch.Tensor | None = None, tensor_cores: bool = True) -> torch.Tensor:
+                     segment_first_position: torch.Tensor | None = None, tensor_cores: bool = True,
+                     window: int = 0, cap: float = 0.0, head_bias: torch.Tensor | None = None) -> torch.Tensor:
     """Causal attention of every row of the step over its request's pages, with the scores or weights changed:
     s_ij = q_i . k_j * scale - r1_h ln(1 + r2_h (i - j)) (``r1``, ``r2`` float32 [n_q]); exp(sink_h) in the
     denominator (``sink`` float32 [n_q]).  q [T, n_q, dk]; k_cache [pages, n_kv, page, dk]; v_cache [.., dv];
     out [T, n_q, dv], or with ``cross`` [T, n_q, n_kv, dv]: head h's weights applied to the values of every
     key/value head.  ``out`` is in the cache's dtype or float32.  ``split`` as for :func:`paged_attention_generic`.
     Given the step's ``segment_start`` (int32 [S + 1]) and ``segment_first_position`` (int32 [S]), bfloat16 shapes that
-    the tensor-core kernel takes run there (``tensor_cores=False``: the general kernel, for comparisons)."""
+    the tensor-core kernel takes run there (``tensor_cores=False``: the general kernel, for comparisons).
+    ``window`` > 0: a row reads its last ``window`` keys only (itself included).  ``cap`` > 0: scores become
+    cap * tanh(s / cap).  ``head_bias`` (float32 [n_q]): no softmax; a key's weight is sigmoid(s + head_bias_h) and the
+    weights are not normalised over the keys."""
     _need_cuda(q, k_cache, v_cache, out, block_tables, segment_of_token, positions, r1, r2, sink, segment_start,
-               segment_first_position)
+               segment_first_position, head_bias)
+    changed = window > 0 or cap > 0.0 or head_bias is not None
     tokens, n_q, dk = q.shape
     n_kv, page_size, dv = k_cache.shape[1], k_cache.shape[2], v_cache.shape[3]
     n_values = n_kv if cross else 1
@@ -833,7 +865,7 @@ def attention_scored(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     assert out.numel() == tokens * n_q * n_values * dv and out.dtype in (q.dtype, torch.float32)
     assert q.dtype == k_cache.dtype == v_cache.dtype and k_cache.shape[3] == dk and v_cache.shape[:3] == k_cache.shape[:3]
     assert block_tables.dtype == torch.int32 and block_tables.dim() == 2 and block_tables.stride(1) == 1
-    for vector in (r1, r2, sink):
+    for vector in (r1, r2, sink, head_bias):
         assert vector is None or (vector.dtype == torch.float32 and vector.shape == (n_q,))
     lib = library.load()
     partials, max_chunks = None, 0
@@ -841,7 +873,7 @@ def attention_scored(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         chunk = int(lib.lse_attention_scored_chunk())
         max_chunks = max(1, -(-(block_tables.stride(0) * page_size) // chunk))
         partials = torch.empty(tokens * n_q * n_values * max_chunks * (dv + 2), dtype=torch.float32, device=q.device)
-    if (tensor_cores and segment_start is not None and segment_first_position is not None
+    if (tensor_cores and not changed and segment_start is not None and segment_first_position is not None
             and attention_scored_mma_supported(dk, dv, n_q, n_kv, q.dtype)):
         segments = segment_first_position.shape[0]
         assert segment_start.dtype == torch.int32 and segment_start.shape[0] == segments + 1 and segments == block_tables.shape[0]
@@ -857,12 +889,12 @@ def attention_scored(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
                                                  n_values, dv, max_chunks, block_tables.shape[0], _stream()),
                   "attention_scored_merge")
         return out
-    check(lib.lse_attention_scored(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), dtype_code(q.dtype),
-                                   int(out.dtype == torch.float32 and q.dtype != torch.float32), block_tables.data_ptr(),
-                                   block_tables.stride(0), segment_of_token.data_ptr(), positions.data_ptr(), _ptr(r1),
-                                   _ptr(r2), _ptr(sink), tokens, n_q, n_kv, dk, dv, int(cross), page_size, float(scale),
-                                   k_cache.shape[0], block_tables.shape[0], _ptr(partials), max_chunks, _stream()),
-          "attention_scored")
+    check(lib.lse_attention_scored_windowed(
+        q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), dtype_code(q.dtype),
+        int(out.dtype == torch.float32 and q.dtype != torch.float32), block_tables.data_ptr(), block_tables.stride(0),
+        segment_of_token.data_ptr(), positions.data_ptr(), _ptr(r1), _ptr(r2), _ptr(sink), tokens, n_q, n_kv, dk, dv,
+        int(cross), page_size, float(scale), k_cache.shape[0], block_tables.shape[0], _ptr(partials), max_chunks,
+        int(window), float(cap), _ptr(head_bias), _stream()), "attention_scored")
     return out
 
 
@@ -963,7 +995,31 @@ def moe_route(logits: torch.Tensor, correction: torch.Tensor | None, outputs: in
     return expert_weights, identity_weight, gate
 
 
-MOE_ACTIVATIONS = {"clamped_swish": 0, "silu": 1}
+def moe_route_sigmoid(logits: torch.Tensor, correction: torch.Tensor | None, experts: int, top: int, group_count: int,
+                      group_keep: int, scale: float, shared_gate: bool = False, chosen: torch.Tensor | None = None):
+    """A router with sigmoid scores, in float32: s = sigmoid(z); the choice goes by s + ``correction`` and is confined to
+    the ``group_keep`` best of ``group_count`` equal groups of neighbouring experts (a group's score: the sum of its two
+    largest choice scores); the ``top`` largest choice scores are chosen; weights s / (sum of the chosen s + 1e-20) *
+    ``scale``.  ``group_count`` <= 1: no groups.  Arguments and results otherwise as :func:`moe_route` (no identity
+    experts: the second result is zeros)."""
+    _need_cuda(logits, correction, chosen)
+    logits, code, n_partials, stride, ld = _projection(logits)
+    tokens = logits.shape[-2]
+    assert code == F32 and logits.shape[-1] >= experts + int(shared_gate)
+    assert correction is None or (correction.dtype == torch.float32 and correction.shape == (experts,))
+    assert chosen is None or (chosen.dtype == torch.int32 and chosen.shape == (tokens, top) and chosen.is_contiguous())
+    expert_weights = torch.empty((tokens, experts), dtype=torch.float32, device=logits.device)
+    identity_weight = torch.empty((tokens,), dtype=torch.float32, device=logits.device)
+    gate = torch.empty((tokens,), dtype=torch.float32, device=logits.device) if shared_gate else None
+    check(library.load().lse_moe_route_sigmoid(logits.data_ptr(), n_partials, stride, ld, _ptr(correction),
+                                               int(shared_gate), expert_weights.data_ptr(), identity_weight.data_ptr(),
+                                               _ptr(gate), _ptr(chosen), tokens, int(experts), int(top), int(group_count),
+                                               int(group_keep), float(scale), _stream()), "moe_route_sigmoid")
+    return expert_weights, identity_weight, gate
+
+
+MOE_ACTIVATIONS = {"clamped_swish": 0, "silu": 1, "squared_relu": 2}
+MOE_UNGATED = frozenset({"squared_relu"})    # activations of experts without a gate: one input column per output column
 
 
 def moe_gated_act(gate_up: torch.Tensor, expert_weights: torch.Tensor, shared_gate: torch.Tensor | None,
@@ -975,11 +1031,13 @@ def moe_gated_act(gate_up: torch.Tensor, expert_weights: torch.Tensor, shared_ga
     the weights are None).  ``gate_up`` is [T, 2 I] (expert by expert [gate | up], then the shared expert's
     [gate | up]) or a float32 stack of partial sums.  ``valid_rows`` (int32, one number on the device): rows from it on
     may be left alone (the unused end of a buffer grouped by expert).  ``activation`` "silu": out = c * silu(g) * u with
-    nothing clamped."""
+    nothing clamped; "squared_relu": experts without a gate, ``gate_up`` is [T, I] (one column per output column) and
+    out = c * relu(u)^2."""
     _need_cuda(gate_up, expert_weights, shared_gate, out, valid_rows)
     tokens, inter = out.shape
-    assert inter == experts * ff + shared_ff and out.is_contiguous() and gate_up.shape[-1] == 2 * inter
-    gate_up, n_partials, stride = _partials(gate_up, tokens, 2 * inter)
+    columns = inter if activation in MOE_UNGATED else 2 * inter
+    assert inter == experts * ff + shared_ff and out.is_contiguous() and gate_up.shape[-1] == columns
+    gate_up, n_partials, stride = _partials(gate_up, tokens, columns)
     assert expert_weights is None or (expert_weights.dtype == torch.float32 and expert_weights.shape == (tokens, experts)
                                       and expert_weights.is_contiguous())
     check(library.load().lse_moe_gated_act_kind(gate_up.data_ptr(), dtype_code(gate_up.dtype), n_partials, stride,
@@ -1110,6 +1168,121 @@ def gated_linear_attention_scan(proj: torch.Tensor, q_off: int, k_off: int, v_of
         take.data_ptr(), float(q_scale), state.data_ptr(), segment_start.data_ptr(), segment_slot.data_ptr(),
         out.data_ptr(), segments, heads, dim, vdim, state.shape[0], chunk_rows, _ptr(chunk_state), max_chunks, _stream()),
         "gated_linear_attention_scan")
+    return out
+
+
+def ssd_gates(proj: torch.Tensor, dt_off: int, dt_bias: torch.Tensor, a_log: torch.Tensor):
+    """(keep, take) float32 [T, heads] of a state-space scan with one decay per head: dt = softplus(proj[:, dt_off + h] +
+    dt_bias[h]) (no clamp), keep = exp(-exp(a_log[h]) dt), take = dt."""
+    _need_cuda(proj, dt_bias, a_log)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens, heads = proj.shape[-2], dt_bias.shape[0]
+    assert dt_bias.dtype == a_log.dtype == torch.float32 and a_log.shape == (heads,)
+    keep = torch.empty((tokens, heads), dtype=torch.float32, device=proj.device)
+    take = torch.empty_like(keep)
+    check(library.load().lse_ssd_gates(proj.data_ptr(), code, n_partials, stride, ld, int(dt_off), dt_bias.data_ptr(),
+                                       a_log.data_ptr(), keep.data_ptr(), take.data_ptr(), tokens, heads, _stream()),
+          "ssd_gates")
+    return keep, take
+
+
+def sigmoid_power(proj: torch.Tensor, off: int, n: int, bias: torch.Tensor | None, tau: float) -> torch.Tensor:
+    """float32 [T, n]: sigmoid(proj[:, off .. off + n] + bias)^(1 / tau), through the logarithm of the sigmoid."""
+    _need_cuda(proj, bias)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = proj.shape[-2]
+    assert bias is None or (bias.dtype == torch.float32 and bias.shape == (n,))
+    keep = torch.empty((tokens, n), dtype=torch.float32, device=proj.device)
+    check(library.load().lse_sigmoid_power(proj.data_ptr(), code, n_partials, stride, ld, int(off), _ptr(bias), float(tau),
+                                           keep.data_ptr(), tokens, int(n), _stream()), "sigmoid_power")
+    return keep
+
+
+def _scan_chunks(tokens: int, segments: int, chunked: bool | None):
+    if chunked if chunked is not None else tokens >= LINEAR_ATTENTION_CHUNKED_FROM:
+        return LINEAR_ATTENTION_CHUNK, tokens // LINEAR_ATTENTION_CHUNK + segments
+    return 0, 0
+
+
+def token_decay_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, keep: torch.Tensor, take: torch.Tensor,
+                     q_scale: float, state: torch.Tensor, segment_start: torch.Tensor, segment_slot: torch.Tensor,
+                     out: torch.Tensor, heads: int, dim: int, vdim: int, qk_share: int = 1,
+                     chunked: bool | None = None) -> torch.Tensor:
+    """S_t = keep[t, h] S_(t-1) + take[t, h] k_t v_t^T, out_t = S_t^T (q_scale q_t), as
+    :func:`gated_linear_attention_scan` without the normaliser's column (state float32 [slots, heads, dim, vdim], out
+    float32 [T, heads * vdim]) and with ``qk_share`` neighbouring heads reading the same q and k columns (head h reads q at
+    q_off + (h // qk_share) * dim): a state-space scan whose inputs B (k) and C (q) belong to groups of heads."""
+    _need_cuda(proj, keep, take, state, segment_start, segment_slot, out)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = proj.shape[-2]
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, dim, vdim)
+    assert keep.dtype == take.dtype == torch.float32 and keep.shape == take.shape == (tokens, heads)
+    assert keep.is_contiguous() and take.is_contiguous() and heads % qk_share == 0
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (tokens, heads * vdim)
+    segments = segment_slot.shape[0]
+    assert segment_start.dtype == segment_slot.dtype == torch.int32 and segment_start.shape[0] == segments + 1
+    chunk_rows, max_chunks = _scan_chunks(tokens, segments, chunked)
+    chunk_state = (torch.empty((max_chunks, heads, dim, vdim), dtype=torch.float32, device=out.device)
+                   if chunk_rows else None)
+    check(library.load().lse_gated_linear_attention_scan_shared(
+        proj.data_ptr(), code, n_partials, stride, ld, int(q_off), int(k_off), int(v_off), keep.data_ptr(),
+        take.data_ptr(), float(q_scale), state.data_ptr(), segment_start.data_ptr(), segment_slot.data_ptr(),
+        out.data_ptr(), segments, heads, dim, vdim, state.shape[0], chunk_rows, _ptr(chunk_state), max_chunks, 0,
+        int(qk_share), _stream()), "token_decay_scan")
+    return out
+
+
+def channel_decay_scan(proj: torch.Tensor, q_off: int, k_off: int, v_off: int, keep: torch.Tensor, q_scale: float,
+                       state: torch.Tensor, segment_start: torch.Tensor, segment_slot: torch.Tensor, out: torch.Tensor,
+                       heads: int, dim: int, vdim: int, chunked: bool | None = None) -> torch.Tensor:
+    """S_t = diag(keep[t, h, :]) S_(t-1) + k_t v_t^T, out_t = S_t^T (q_scale q_t): a decay per row of the state (per key
+    channel), token and head; keep float32 [T, heads * dim]; state float32 [slots, heads, dim, vdim]; out float32
+    [T, heads * vdim].  ``chunked`` as for :func:`linear_attention_scan`."""
+    _need_cuda(proj, keep, state, segment_start, segment_slot, out)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens = proj.shape[-2]
+    assert state.dtype == torch.float32 and state.is_contiguous() and state.shape[1:] == (heads, dim, vdim)
+    assert keep.dtype == torch.float32 and keep.shape == (tokens, heads * dim) and keep.is_contiguous()
+    assert out.dtype == torch.float32 and out.is_contiguous() and out.shape == (tokens, heads * vdim)
+    segments = segment_slot.shape[0]
+    assert segment_start.dtype == segment_slot.dtype == torch.int32 and segment_start.shape[0] == segments + 1
+    chunk_rows, max_chunks = _scan_chunks(tokens, segments, chunked)
+    chunk_state = chunk_keep = None
+    if chunk_rows:
+        chunk_state = torch.empty((max_chunks, heads, dim, vdim), dtype=torch.float32, device=out.device)
+        chunk_keep = torch.empty((max_chunks, heads, dim), dtype=torch.float32, device=out.device)
+    check(library.load().lse_vector_decay_attention_scan(
+        proj.data_ptr(), code, n_partials, stride, ld, int(q_off), int(k_off), int(v_off), keep.data_ptr(), float(q_scale),
+        state.data_ptr(), segment_start.data_ptr(), segment_slot.data_ptr(), out.data_ptr(), segments, heads, dim, vdim,
+        state.shape[0], chunk_rows, _ptr(chunk_state), max_chunks, _ptr(chunk_keep), _stream()), "channel_decay_scan")
+    return out
+
+
+def gated_group_rmsnorm(values: torch.Tensor, proj: torch.Tensor, g_off: int, weight: torch.Tensor, eps: float,
+                        out: torch.Tensor, groups: int, gate_first: bool, gate_activation: str = "silu",
+                        scale: float = 1.0, skip: torch.Tensor | None = None, skip_source: torch.Tensor | None = None,
+                        skip_offset: int = 0, segment_of_token: torch.Tensor | None = None) -> torch.Tensor:
+    """The norm behind a scan, in ``groups`` equal parts of a row, each by its own root mean square.  With a = values
+    (+ skip[head] * x, x the columns ``skip_offset`` .. of ``skip_source``, a head being n / len(skip) columns) and g
+    the columns ``g_off`` .. of ``proj`` through ``gate_activation`` ("silu" or "sigmoid"):
+    ``gate_first``: b = a g, out = b / rms(b) * weight * scale; else out = a / rms(a) * weight * g * scale.
+    ``weight`` float32 of any length that divides n, read at column % length (a weight per part shared by the parts).
+    ``out`` [T, n] in the compute dtype; its rows may be strided (a column range of a wider tensor)."""
+    _need_cuda(values, proj, weight, out, skip, skip_source, segment_of_token)
+    proj, code, n_partials, stride, ld = _projection(proj)
+    tokens, n = values.shape
+    assert values.dtype == torch.float32 and values.is_contiguous() and weight.dtype == torch.float32
+    assert n % groups == 0 and n % weight.shape[0] == 0 and out.shape == (tokens, n) and out.stride(1) == 1
+    x_ld = head_width = 0
+    if skip is not None:
+        assert skip.dtype == torch.float32 and n % skip.shape[0] == 0 and skip_source.dtype == out.dtype
+        assert skip_source.dim() == 2 and skip_source.stride(1) == 1
+        x_ld, head_width = skip_source.stride(0), n // skip.shape[0]
+    check(library.load().lse_gated_group_rmsnorm(
+        values.data_ptr(), proj.data_ptr(), code, n_partials, stride, ld, int(g_off), _ptr(skip_source), x_ld,
+        int(skip_offset), _ptr(skip), head_width, weight.data_ptr(), weight.shape[0], out.data_ptr(), dtype_code(out.dtype),
+        out.stride(0), tokens, n, int(groups), float(eps), float(scale), int(gate_first),
+        {"sigmoid": 0, "silu": 1}[gate_activation], _ptr(segment_of_token), _stream()), "gated_group_rmsnorm")
     return out
 
 

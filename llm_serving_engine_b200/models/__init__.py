@@ -3,7 +3,7 @@ from __future__ import annotations
 
 import torch
 
-from . import fororax, givelix, qwen2, tufevik  # noqa: F401  (register Fororax, Givelix, Qwen2ForCausalLM and Tufevik)
+from . import fororax, givelix, qwen2, sebudra, tufevik  # noqa: F401  (register Fororax, Givelix, Qwen2ForCausalLM, Sebudra and Tufevik)
 from .decoder import DecoderModel, cache_requirements, expected_tensors
 
 _DTYPES = {"bfloat16": torch.bfloat16, "bf16": torch.bfloat16, "float32": torch.float32, "fp32": torch.float32}

@@ -24,7 +24,7 @@ def _layer_part_prefixes(layer: LayerSpec) -> dict[str, str]:
 
 def _layer_parts(layer: LayerSpec) -> list[tuple[str, type, PartSpec] | None]:
     """(tensor prefix, class, description) of the four parts of a layer, in the order a block is built from;
-    None for the feed-forward and its norm of a layer that has none."""
+    None for the feed-forward and its norm of a layer that has none, and for a norm that the arrangement does without."""
     prefixes = _layer_part_prefixes(layer)
     found = [
         (prefixes["mixer_norm"], NORMS.get(layer.mixer_norm.kind), layer.mixer_norm),
@@ -32,8 +32,9 @@ def _layer_parts(layer: LayerSpec) -> list[tuple[str, type, PartSpec] | None]:
     ]
     if layer.feed_forward is None:
         return found + [None, None]
+    norm = layer.feed_forward_norm     # None: an arrangement whose feed-forward reads the mixer's norm
     return found + [
-        (prefixes["feed_forward_norm"], NORMS.get(layer.feed_forward_norm.kind), layer.feed_forward_norm),
+        None if norm is None else (prefixes["feed_forward_norm"], NORMS.get(norm.kind), norm),
         (prefixes["feed_forward"], FEED_FORWARDS.get(layer.feed_forward.kind), layer.feed_forward),
     ]
 

@@ -5,6 +5,7 @@ import torch
 
 from ..weights.tensor_spec import TensorSpec
 from .base import NORMS, Block, ResidualStream, register_block
+from .linear import stack_sums
 
 
 @register_block("prenorm_residual")
@@ -137,3 +138,21 @@ class SandwichResidualBlock(Block):
             x = self.feed_forward_norm.forward(stream)
             stream.delta = self.feed_forward.forward(x)
             stream.delta_norm = self.feed_forward_after
+
+
+@register_block("parallel_residual")
+class ParallelResidualBlock(Block):
+    """n = norm(h); h = h + mixer(n) + feed_forward(n): one norm, both sublayers read its output, and the residual takes
+    their sum.  The two outputs stay pending in the stream as one float32 stack of sums (each sublayer's partial sums
+    one after the other), which the next norm adds up in float32 before the residual is touched.  A layer may have no
+    feed-forward; a feed-forward norm is not used."""
+
+    graph_safe = True
+
+    def forward(self, stream: ResidualStream, step, cache) -> None:
+        x = self.mixer_norm.forward(stream)
+        mixed = self.mixer.forward(x, step, cache)
+        if self.feed_forward is None:
+            stream.delta = mixed
+        else:
+            stream.delta = stack_sums(mixed, self.feed_forward.forward(x))

@@ -8,7 +8,7 @@ from ..kernels import ops
 from ..weights.tensor_spec import TensorSpec
 from .base import MIXERS, Mixer, PagedKV, RequestState, cache_for, cache_needs, register_mixer
 from .latent_attention import rotary_frequencies
-from .linear import linear_partials
+from .linear import linear_partials, linear_sums
 from .mlstm import input_projection
 from .normed_attention import prompt_shape_for_tcgen05
 
@@ -200,10 +200,177 @@ class SelectiveStateSpace(BranchMixer):
                            self.skip, state, step, out, scale)
 
 
+_HEAD_NORM_NAMES = {"q": "q", "k": "k", "v": "v", "out": "o", "q_norm": "q.norm", "k_norm": "k.norm",
+                    "bias_suffix": ".b", "head_bias": "pb"}
+
+
+@register_mixer("head_norm_rotary_attention")
+class HeadNormRotaryAttention(BranchMixer):
+    """params: ``heads``, ``kv_heads`` (query head h uses key/value head h // (heads / kv_heads)), ``dim`` (of a head's
+    query and key), ``vdim`` (of its value), ``eps``, ``scale`` (on the scores), ``bias`` (q, k and v projections have
+    bias vectors), ``rot`` ({base, dims, scaling} or None: the first ``dims`` values of every head are rotated, value i
+    paired with i + dims / 2; see ``rotary_frequencies`` for ``scaling``), ``window`` (> 0: a row reads its last
+    ``window`` keys, itself included; older pages are given back), ``softcap`` (> 0: scores become cap * tanh(s / cap)),
+    ``weights`` ("softmax", the default, or "sigmoid": a key's weight is sigmoid(score + b_h) with a learned number per
+    head, not normalised over the keys), ``tensor_names``.
+
+    Every head of q and of k is RMS-normed over its ``dim`` values with one weight vector for all heads, before the
+    rotation.  One kernel sums the projection, adds the biases, norms, rotates and writes the pages; the attention is
+    the engine's paged attention for changed scores (window, cap and sigmoid weights are arguments of its kernels)."""
+
+    graph_safe = True
+
+    def __init__(self, params, weights, ctx) -> None:
+        super().__init__(params, weights, ctx)
+        p = params
+        self.n_q, self.n_kv, self.dk, self.dv = int(p["heads"]), int(p["kv_heads"]), int(p["dim"]), int(p["vdim"])
+        self.scale, self.eps = float(p["scale"]), float(p["eps"])
+        self.window, self.softcap = int(p.get("window", 0)), float(p.get("softcap", 0.0))
+        self.sigmoid = self._weights_kind(p) == "sigmoid"
+        if self.n_q % self.n_kv:
+            raise ops.KernelError(f"attention: {self.n_q} query heads do not divide into {self.n_kv} groups")
+        rot = p.get("rot") or {"dims": 0, "base": 1.0}
+        if int(rot["dims"]) % 2 or int(rot["dims"]) > self.dk:
+            raise ops.KernelError(f"attention: {rot['dims']} rotated values of {self.dk}")
+        freq, self.rot_factor = rotary_frequencies(rot) if int(rot["dims"]) else (torch.zeros(0, dtype=torch.float64), 1.0)
+        self.freq = freq.to(torch.float64).contiguous().to(ctx.device)
+        names = {**_HEAD_NORM_NAMES, **p.get("tensor_names", {})}
+        roles = ("q", "k", "v")
+        self.in_weight = torch.cat([weights[names[role]] for role in roles], dim=0).contiguous()
+        self.in_bias = (torch.cat([weights[names[role] + names["bias_suffix"]].to(torch.float32) for role in roles]).contiguous()
+                        if p.get("bias", False) else None)
+        self.q_norm = weights[names["q_norm"]].to(torch.float32).contiguous()
+        self.k_norm = weights[names["k_norm"]].to(torch.float32).contiguous()
+        self.head_bias = weights[names["head_bias"]].to(torch.float32).contiguous() if self.sigmoid else None
+        self.out_weight = weights[names["out"]].contiguous()
+
+    @staticmethod
+    def _weights_kind(params) -> str:
+        kind = params.get("weights", "softmax")
+        if kind not in ("softmax", "sigmoid"):
+            raise ops.KernelError(f"attention: weights {kind!r} must be softmax or sigmoid")
+        return kind
+
+    @classmethod
+    def expected_tensors(cls, params, hidden_size):
+        p = params
+        n_q, n_kv, dk, dv = int(p["heads"]), int(p["kv_heads"]), int(p["dim"]), int(p["vdim"])
+        names = {**_HEAD_NORM_NAMES, **p.get("tensor_names", {})}
+        out = {names["q"]: TensorSpec((n_q * dk, hidden_size)), names["k"]: TensorSpec((n_kv * dk, hidden_size)),
+               names["v"]: TensorSpec((n_kv * dv, hidden_size)), names["out"]: TensorSpec((hidden_size, n_q * dv)),
+               names["q_norm"]: TensorSpec((dk,), "norm"), names["k_norm"]: TensorSpec((dk,), "norm")}
+        if p.get("bias", False):
+            for role in ("q", "k", "v"):
+                out[names[role] + names["bias_suffix"]] = TensorSpec((out[names[role]].shape[0],), "bias")
+        if cls._weights_kind(p) == "sigmoid":
+            out[names["head_bias"]] = TensorSpec((n_q,), "bias")
+        return out
+
+    @classmethod
+    def cache_requirement(cls, params, hidden_size):
+        dk, dv = int(params["dim"]), int(params["vdim"])
+        return PagedKV(int(params["kv_heads"]), dk, int(params.get("window", 0)), 0 if dv == dk else dv)
+
+    def launch_signature(self, segment_counts):
+        return ()
+
+    def inner(self, proj, offset, step, cache, out, scale):
+        pages = cache
+        tokens = out.shape[0]
+        q = torch.empty((tokens, self.n_q, self.dk), dtype=out.dtype, device=out.device)
+        ops.head_norm_rope_kv_write(proj, self.in_bias, self.q_norm, self.k_norm, self.eps, pages.slot_mapping,
+                                    step.positions, self.freq, self.rot_factor, q, pages.keys, pages.values, self.n_q,
+                                    self.n_kv, self.dk, self.dv, offset=offset)
+        attended = torch.empty((tokens, self.n_q, self.dv), dtype=out.dtype, device=out.device)
+        ops.attention_scored(q, pages.keys, pages.values, attended, pages.block_tables, step.segment_of_token,
+                             step.positions, self.scale, segment_start=step.segment_start,
+                             segment_first_position=step.segment_first_position, window=self.window, cap=self.softcap,
+                             head_bias=self.head_bias)
+        ops.head_gate_scale(attended, None, out, scale, step.segment_of_token)
+
+
+_SSD_NAMES = {"in": "in", "conv": "conv", "conv_bias": "conv.b", "dt_bias": "dt_bias", "a_log": "A_log", "skip": "D",
+              "norm": "norm", "out": "o"}
+
+
+@register_mixer("grouped_state_space")
+class GroupedStateSpace(BranchMixer):
+    """params: ``heads``, ``vdim`` (channels of a head; inner = heads * vdim), ``state`` (N, rows of a head's state),
+    ``groups`` (head h reads the B and C of group h // (heads / groups)), ``conv`` (taps), ``norm_groups`` (equal parts of
+    the inner width that the output norm takes one by one), ``eps``, ``tensor_names``.
+
+    A state-space scan with one decay per head and token (the duality form).  W_in x = [z (inner) | u (inner) | B (groups *
+    N) | C (groups * N) | dt (heads)]; [u | B | C] pass a short causal convolution per channel (with bias) and SiLU;
+    dt <- softplus(dt + dt_bias) without a clamp; per head
+        S <- exp(-exp(A_log_h) dt) S + dt B u^T      (S is [N, vdim]),        y = S^T C + D_h u;
+    the output is W_out (rmsnorm_in_parts(y * silu(z)) * w): the gate comes before the norm.  Kept per request, in
+    float32: S [heads, N, vdim] and the last ``conv - 1`` rows of [u | B | C] before the convolution.  Step sizes, decays
+    and the state are float32.  The scan is the engine's matrix-memory scan with a keep and a take factor per token and
+    head, its keys and queries shared by the heads of a group."""
+
+    graph_safe = True
+
+    def __init__(self, params, weights, ctx) -> None:
+        super().__init__(params, weights, ctx)
+        p = params
+        self.heads, self.vdim, self.states, self.groups = int(p["heads"]), int(p["vdim"]), int(p["state"]), int(p["groups"])
+        self.taps, self.norm_groups, self.eps = int(p["conv"]), int(p.get("norm_groups", 1)), float(p["eps"])
+        self.inner_width = self.heads * self.vdim
+        self.channels = self.inner_width + 2 * self.groups * self.states
+        if self.heads % self.groups or self.inner_width % self.norm_groups:
+            raise ops.KernelError(f"state space: {self.heads} heads, {self.groups} groups, {self.norm_groups} norm parts")
+        names = {**_SSD_NAMES, **p.get("tensor_names", {})}
+        self.in_weight = weights[names["in"]].contiguous()
+        self.conv_weight = weights[names["conv"]].to(torch.float32).contiguous()
+        self.conv_bias = weights[names["conv_bias"]].to(torch.float32).contiguous()
+        self.dt_bias = weights[names["dt_bias"]].to(torch.float32).contiguous()
+        self.a_log = weights[names["a_log"]].to(torch.float32).contiguous()
+        self.skip = weights[names["skip"]].to(torch.float32).contiguous()
+        self.norm_weight = weights[names["norm"]].to(torch.float32).contiguous()
+        self.out_weight = weights[names["out"]].contiguous()
+
+    @classmethod
+    def expected_tensors(cls, params, hidden_size):
+        p = params
+        heads, vdim, states, groups, taps = int(p["heads"]), int(p["vdim"]), int(p["state"]), int(p["groups"]), int(p["conv"])
+        inner, channels = heads * vdim, heads * vdim + 2 * groups * states
+        names = {**_SSD_NAMES, **p.get("tensor_names", {})}
+        return {names["in"]: TensorSpec((inner + channels + heads, hidden_size)),
+                names["conv"]: TensorSpec((channels, taps), "filter"), names["conv_bias"]: TensorSpec((channels,), "bias"),
+                names["dt_bias"]: TensorSpec((heads,), "bias"), names["a_log"]: TensorSpec((heads,), "bias"),
+                names["skip"]: TensorSpec((heads,), "norm"), names["norm"]: TensorSpec((inner,), "norm"),
+                names["out"]: TensorSpec((hidden_size, inner))}
+
+    @classmethod
+    def cache_requirement(cls, params, hidden_size):
+        heads, vdim, states, groups, taps = (int(params[key]) for key in ("heads", "vdim", "state", "groups", "conv"))
+        channels = heads * vdim + 2 * groups * states
+        return (RequestState((heads, states, vdim), "float32"), RequestState((max(taps - 1, 0), channels), "float32"))
+
+    def inner(self, proj, offset, step, cache, out, scale):
+        state, window = cache.parts[0].state, cache.parts[1].state
+        tokens = out.shape[0]
+        inner = self.inner_width
+        u = torch.empty((tokens, self.channels), dtype=out.dtype, device=out.device)
+        ops.short_conv_act(proj, offset + inner, self.conv_weight, self.conv_bias, window, step, u, "silu")
+        if self.taps > 1:
+            ops.short_conv_state(proj, offset + inner, self.channels, self.taps, window, step)
+        keep, take = ops.ssd_gates(proj, offset + inner + self.channels, self.dt_bias, self.a_log)
+        read = torch.empty((tokens, inner), dtype=torch.float32, device=out.device)
+        b_off = inner
+        c_off = inner + self.groups * self.states
+        ops.token_decay_scan(u, c_off, b_off, 0, keep, take, 1.0, state, step.segment_start, step.segment_state_slot,
+                             read, self.heads, self.states, self.vdim, qk_share=self.heads // self.groups)
+        ops.gated_group_rmsnorm(read, proj, offset, self.norm_weight, self.eps, out, self.norm_groups, gate_first=True,
+                                gate_activation="silu", scale=scale, skip=self.skip, skip_source=u, skip_offset=0,
+                                segment_of_token=step.segment_of_token)
+
+
 @register_mixer("parallel_mixers")
 class ParallelMixers(Mixer):
     """params: ``branches``: a list of {"kind" (a registered mixer of the ``BranchMixer`` form), "params", "prefix" (of
-    its tensors after this part's), "scale"}.
+    its tensors after this part's), "scale"}; ``float32_output`` (the output product leaves float32 sums whatever the
+    compute dtype: for layers that add this output to another branch's before the residual takes it).
 
     y = sum_b scale_b * branch_b(x): every branch reads the same x.  The branches' input matrices are stacked into
     one product and their output matrices laid side by side, each branch writing scale_b times its activations into
@@ -215,6 +382,7 @@ class ParallelMixers(Mixer):
     def __init__(self, params, weights, ctx) -> None:
         super().__init__(params, weights, ctx)
         self.branches, self.scales, self.needs = [], [], []
+        self.float32_output = bool(params.get("float32_output", False))
         for branch in params["branches"]:
             cls = MIXERS.get(branch["kind"])
             if not issubclass(cls, BranchMixer):
@@ -264,4 +432,4 @@ class ParallelMixers(Mixer):
             branch.inner(proj, self.in_offsets[index], step, cache_for(cache, self.needs[index], first), view,
                          self.scales[index])
             first += self.needs[index]
-        return linear_partials(mid, self.out_weight)
+        return linear_sums(mid, self.out_weight) if self.float32_output else linear_partials(mid, self.out_weight)

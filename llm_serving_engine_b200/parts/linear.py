@@ -65,3 +65,21 @@ def linear(x: torch.Tensor, weight: torch.Tensor, bias: torch.Tensor | None = No
         return y if bias is None else y + bias
     y = torch.mm(x, weight.t())
     return y if bias is None else y + bias.to(y.dtype)
+
+
+def linear_sums(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
+    """x W^T with float32 results whatever the compute dtype: a stack of partial sums for few rows, else one float32
+    tensor.  For projections that feed a recurrence or a gate, and for branch outputs that are added to another
+    branch's before the residual takes them: they stay float32 from the product's sums on."""
+    if x.dtype == torch.bfloat16:
+        if x.shape[0] <= SKINNY_MAX_ROWS and ops.gemm_bf16_skinny_ok(x, weight):
+            return ops.gemm_bf16_skinny(x, weight)
+        return torch.mm(x, weight.t(), out_dtype=torch.float32)
+    return linear_partials(x, weight)
+
+
+def stack_sums(first: torch.Tensor, second: torch.Tensor) -> torch.Tensor:
+    """Two branch outputs ([rows, out], or float32 stacks of partial sums [P, rows, out]) as one float32 stack whose
+    sum is the sum of both: the consumer adds the members in index order, in float32."""
+    members = [y if y.dim() == 3 else y.unsqueeze(0) for y in (first, second)]
+    return torch.cat([y if y.dtype == torch.float32 else y.to(torch.float32) for y in members], dim=0)

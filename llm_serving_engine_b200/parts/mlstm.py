@@ -6,7 +6,7 @@ import torch
 from ..kernels import ops
 from ..weights.tensor_spec import TensorSpec
 from .base import Mixer, RequestState, register_mixer
-from .linear import linear_partials, SKINNY_MAX_ROWS
+from .linear import linear_sums, linear_partials, SKINNY_MAX_ROWS
 
 _DEFAULT_NAMES = {"q": "q", "k": "k", "v": "v", "gate": "g", "out": "o", "norm": "norm", "input_gate": "i",
                   "forget_gate": "f", "bias_suffix": ".b"}
@@ -91,10 +91,5 @@ class MatrixMemory(Mixer):
 
 
 def input_projection(x: torch.Tensor, weight: torch.Tensor) -> torch.Tensor:
-    """x W^T with float32 results whatever the compute dtype: a stack of partial sums for few rows, else one float32
-    tensor.  For mixers whose projections feed a recurrence or a gate, which stay float32 from the product's sums on."""
-    if x.dtype == torch.bfloat16:
-        if x.shape[0] <= SKINNY_MAX_ROWS and ops.gemm_bf16_skinny_ok(x, weight):
-            return ops.gemm_bf16_skinny(x, weight)
-        return torch.mm(x, weight.t(), out_dtype=torch.float32)
-    return linear_partials(x, weight)
+    """x W^T with float32 results whatever the compute dtype (``parts.linear.linear_sums``)."""
+    return linear_sums(x, weight)

@@ -27,7 +27,11 @@ class ClampedMoE(FeedForward):
     sigmoid(w_sg . x)), ``router_bias`` (the router's logits have a bias vector; default false), ``weights``
     ("softmax_all", the default below, or "softmax_chosen": the ``top`` largest logits are chosen and the weights are
     the softmax over the chosen logits only), ``activation`` ("clamped_swish", the default below, or "silu":
-    y = W_down (silu(W_gate x) * (W_up x)), nothing clamped, ``limit`` not read), ``tensor_names``.
+    y = W_down (silu(W_gate x) * (W_up x)), nothing clamped, ``limit`` not read; or "squared_relu": experts without a
+    gate matrix, y = W_down relu(W_up x)^2), ``scores`` ("softmax", the default, or "sigmoid": scores are sigmoids of the
+    logits, the chosen experts' scores are divided by their sum and multiplied by ``router_scale``, and with ``groups``
+    {"count", "keep"} the choice is confined to the ``keep`` best of ``count`` equal groups of neighbouring experts, a
+    group's score being the sum of its two largest corrected scores), ``tensor_names``.
 
     Expert: g = min(W_gate x, limit), u = clamp(W_up x, -limit, limit), y = W_down (g sigmoid(1.702 g) (u + 1)).
     Router: s = softmax(W_router x) over all outputs, in float32; the ``top`` outputs with the largest s + correction
@@ -56,15 +60,25 @@ class ClampedMoE(FeedForward):
         if p.get("weights", "softmax_all") not in ("softmax_all", "softmax_chosen"):
             raise ops.KernelError(f"mixture of experts: weights {p.get('weights')!r} must be softmax_all or softmax_chosen")
         self.over_chosen = p.get("weights", "softmax_all") == "softmax_chosen"
+        if p.get("scores", "softmax") not in ("softmax", "sigmoid"):
+            raise ops.KernelError(f"mixture of experts: scores {p.get('scores')!r} must be softmax or sigmoid")
+        self.sigmoid_scores = p.get("scores", "softmax") == "sigmoid"
+        groups = p.get("groups") or {}
+        self.group_count, self.group_keep = int(groups.get("count", 1)), int(groups.get("keep", 1))
+        self.router_scale = float(p.get("router_scale", 1.0))
+        if self.sigmoid_scores and (self.identity or self.over_chosen or p.get("router_bias", False)):
+            raise ops.KernelError("mixture of experts: sigmoid scores come without identity experts, a router bias or softmax_chosen")
+        self.columns = 1 if self.activation in ops.MOE_UNGATED else 2    # input columns per column of an expert
         self.ff, self.limit = int(p["ff"]), float(p.get("limit", 0.0))
         shared = p.get("shared")
         self.shared_ff = int(shared["ff"]) if shared else 0
-        self.shared_limit = float(shared["limit"]) if shared else 0.0
+        self.shared_limit = float(shared.get("limit", 0.0)) if shared else 0.0
         names = {**_DEFAULT_NAMES, **p.get("tensor_names", {})}
         prefixes = [names["expert"].format(index=index) for index in range(self.experts)]
         if shared:
             prefixes.append(names["shared"])
-        pairs = [weights[prefix + names[which]] for prefix in prefixes for which in ("gate", "up")]
+        roles = ("up",) if self.columns == 1 else ("gate", "up")
+        pairs = [weights[prefix + names[which]] for prefix in prefixes for which in roles]
         self.inter = self.experts * self.ff + self.shared_ff
         self.gate_up_weight = torch.cat(pairs, dim=0).contiguous() if prefixes else None
         self.down_weight = torch.cat([weights[prefix + names["down"]] for prefix in prefixes], dim=1).contiguous() if prefixes else None
@@ -85,7 +99,8 @@ class ClampedMoE(FeedForward):
         if (self.experts and self.gate_up_weight.dtype == torch.bfloat16 and width % 8 == 0 and self.ff % 8 == 0
                 and self.inter % 8 == 0 and hasattr(torch, "_grouped_mm")):
             routed = self.experts * self.ff
-            self._grouped_gate_up = self.gate_up_weight[:2 * routed].view(self.experts, 2 * self.ff, width).transpose(1, 2)
+            self._grouped_gate_up = (self.gate_up_weight[:self.columns * routed]
+                                     .view(self.experts, self.columns * self.ff, width).transpose(1, 2))
             self._grouped_down = self.down_weight.as_strided((self.experts, self.ff, width), (self.ff, 1, self.inter))
 
     @classmethod
@@ -102,8 +117,10 @@ class ClampedMoE(FeedForward):
         if p.get("shared"):
             sized.append((names["shared"], int(p["shared"]["ff"])))
             out[names["shared"] + names["shared_gate"]] = TensorSpec((1, hidden_size))
+        gated = p.get("activation", "clamped_swish") not in ops.MOE_UNGATED
         for prefix, width in sized:
-            out[prefix + names["gate"]] = TensorSpec((width, hidden_size))
+            if gated:
+                out[prefix + names["gate"]] = TensorSpec((width, hidden_size))
             out[prefix + names["up"]] = TensorSpec((width, hidden_size))
             out[prefix + names["down"]] = TensorSpec((hidden_size, width))
         return out
@@ -116,9 +133,10 @@ class ClampedMoE(FeedForward):
         y = None
         if self.shared_ff:   # the shared expert: two plain products, its gate folded into the activation
             routed = self.experts * self.ff
-            gate_up = linear(x, self.gate_up_weight[2 * routed:])
+            gate_up = linear(x, self.gate_up_weight[self.columns * routed:])
             act = torch.empty((tokens, self.shared_ff), dtype=x.dtype, device=x.device)
-            ops.moe_gated_act(gate_up, None, shared_gate, act, 0, 8, self.shared_ff, self.limit, self.shared_limit)
+            ops.moe_gated_act(gate_up, None, shared_gate, act, 0, 8, self.shared_ff, self.limit, self.shared_limit,
+                              activation=self.activation)
             y = linear(act, self.down_weight[:, routed:], out_dtype=torch.float32)
         row_of, offsets = ops.moe_group_rows(chosen, self.experts)
         rows = tokens * self.top
@@ -141,6 +159,9 @@ class ClampedMoE(FeedForward):
             logits = ops.gemm_bf16_skinny(x, self.router)     # float32 partial sums, added up by the routing kernel
         else:
             logits = linear(x, self.router, out_dtype=torch.float32)
+        if self.sigmoid_scores:
+            return ops.moe_route_sigmoid(logits, self.correction, self.experts, self.top, self.group_count,
+                                         self.group_keep, self.router_scale, shared_gate=self.shared_ff > 0, chosen=chosen)
         return ops.moe_route(logits, self.correction, self.outputs, self.identity, self.top,
                              shared_gate=self.shared_ff > 0, chosen=chosen, logit_bias=self.router_bias,
                              over_chosen=self.over_chosen)

@@ -24,6 +24,7 @@ RANDOM_MODELS = {
     "givelix": dict(vocab_size=260),     # the Givelix design at a small size (``_givelix_stand_in``)
     "fororax": dict(vocab_size=260),     # the Fororax design at a small size (``_fororax_stand_in``)
     "tufevik": dict(vocab_size=260),     # the Tufevik design at a small size (``_tufevik_stand_in``)
+    "sebudra": dict(vocab_size=260),     # the Sebudra design at a small size (``_sebudra_stand_in``)
     # the reference's ModelConfig.tiny (src/llmserve/config.py:34-44) over the byte tokenizer's vocabulary
     "tiny": dict(vocab_size=260, hidden_size=128, intermediate_size=352, num_hidden_layers=4, num_attention_heads=4,
                  num_key_value_heads=2, max_position_embeddings=1024, rope_theta=10000.0, rms_norm_eps=1e-6),
@@ -77,8 +78,32 @@ def _tufevik_stand_in(vocab_size: int) -> dict:
                        {"type": "mlstm", "mixer": memory, "mlp": mlp}]}
 
 
+def _sebudra_stand_in(vocab_size: int) -> dict:
+    """A small model of the Sebudra design: a layer with a windowed attention and a state-space scan side by side over a
+    dense feed-forward, a sigmoid-weighted attention over a mixture of experts, a matrix memory with a decay per key
+    channel, and the first layer once more with its tensors and a cache of its own."""
+    mlp = {"kind": "moe", "router": {"experts": 6, "top": 2, "scale": 1.5, "groups": {"count": 3, "keep": 2}},
+           "expert": {"ff": 96}, "shared": {"ff": 128}}
+    dense = {"kind": "dense", "ff": 352, "limit": 3.0}
+    left = {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 32 ** -0.5, "mask": {"size": 48},
+            "rot": {"base": 10000.0, "dims": 16, "scaling": {"factor": 4.0, "original": 256, "fast": 16.0, "slow": 1.0}}}
+    right = {"heads": 4, "vdim": 32, "state": 16, "groups": 2, "conv": 4, "norm_groups": 2}
+    first = {"type": "parallel", "mlp": dense,
+             "mixer": {"left": left, "right": right, "left_scale": 0.5, "right_scale": 0.5}}
+    return {"architecture": "Sebudra", "vocab": vocab_size, "width": 128, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 128 ** 0.5}, "max_position_embeddings": 1024,
+            "layers": [first,
+                       {"type": "attention", "mlp": mlp,
+                        "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 32 ** -0.5, "softcap": 20.0,
+                                  "rot": {"base": 10000.0, "dims": 32}}},
+                       {"type": "gla", "mlp": mlp, "mixer": {"heads": 4, "dim": 32, "vdim": 32, "tau": 16.0, "rank": 16}},
+                       dict(first, weights_of=0)]}
+
+
 def tiny_config(vocab_size: int = 260, name: str = "tiny") -> dict:
     """config.json of a random stand-in model."""
+    if name == "sebudra":
+        return _sebudra_stand_in(vocab_size)
     if name == "tufevik":
         return _tufevik_stand_in(vocab_size)
     if name == "fororax":

@@ -571,7 +571,19 @@ TUFEVIK_SIZES = {
     "w2048": dict(width=2048, heads=16, ff=8192),
     "w4096": dict(width=4096, heads=32, ff=16384),
 }
-DESIGN_SIZES = {"givelix": GIVELIX_SIZES, "fororax": FORORAX_SIZES, "tufevik": TUFEVIK_SIZES}
+# Sebudra at layer sizes that resemble real models of the kind: six layers in the order [side by side, sigmoid attention,
+# matrix memory with channel decays, side by side, sigmoid attention, matrix memory]; attention heads of 128 in groups of
+# eight (the windowed one over 512 keys, half of a head rotated with stretched frequencies); a state-space scan of as
+# many channels as the model is wide in heads of 64 with 128 state rows and two groups, four taps; a matrix memory with
+# heads of 64 key channels and 128 values and a decay map of rank 16; dense feed-forwards and mixtures of eight ungated
+# experts in four groups (two kept) of half the dense size of which a token uses two, beside a shared expert of the same
+# size, so that a token's feed-forward work equals the gated dense layer's.  The closest existing model is Tufevik (an
+# attention and a scan side by side, a matrix memory, mixtures of experts): it is measured beside it at equal size.
+SEBUDRA_SIZES = {
+    "w2048": dict(width=2048, heads=16, ff=8192),
+    "w4096": dict(width=4096, heads=32, ff=16384),
+}
+DESIGN_SIZES = {"givelix": GIVELIX_SIZES, "fororax": FORORAX_SIZES, "tufevik": TUFEVIK_SIZES, "sebudra": SEBUDRA_SIZES}
 
 
 def fororax_config(width: int, heads: int, ff: int, vocab: int = 32768, context: int = 4096) -> dict:
@@ -598,6 +610,25 @@ def tufevik_config(width: int, heads: int, ff: int, vocab: int = 32768, context:
               {"type": "mlstm", "mixer": memory, "mlp": mixture}, {"type": "parallel", "mixer": side_by_side, "mlp": dense},
               {"type": "mlstm", "mixer": memory, "mlp": dense}, {"type": "parallel", "mixer": side_by_side, "mlp": mixture}]
     return {"architecture": "Tufevik", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-6},
+            "embedding": {"scale": 1.0}, "max_position_embeddings": context}
+
+
+def sebudra_config(width: int, heads: int, ff: int, vocab: int = 32768, context: int = 4096) -> dict:
+    dense = {"kind": "dense", "ff": ff, "limit": 7.0}
+    mixture = {"kind": "moe", "router": {"experts": 8, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+               "expert": {"ff": ff // 2}, "shared": {"ff": ff // 2}}
+    kv_heads = max(2, heads // 8)
+    left = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 512},
+            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 1.0}}}
+    right = {"heads": width // 64, "vdim": 64, "state": 128, "groups": 2, "conv": 4, "norm_groups": 2}
+    side_by_side = {"left": left, "right": right, "left_scale": 0.5, "right_scale": 0.5}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
+                 "rot": {"base": 250000.0, "dims": 128}}
+    memory = {"heads": heads, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 16}
+    layers = [{"type": "parallel", "mixer": side_by_side, "mlp": dense}, {"type": "attention", "mixer": attention, "mlp": mixture},
+              {"type": "gla", "mixer": memory, "mlp": mixture}, {"type": "parallel", "mixer": side_by_side, "mlp": dense},
+              {"type": "attention", "mixer": attention, "mlp": dense}, {"type": "gla", "mixer": memory, "mlp": mixture}]
+    return {"architecture": "Sebudra", "vocab": vocab, "width": width, "layers": layers, "norm": {"eps": 1e-6},
             "embedding": {"scale": 1.0}, "max_position_embeddings": context}
 
 
@@ -649,8 +680,12 @@ def run_design(args) -> dict:
     peak = peaks()
     fma_tflops = 2 * 128 * torch.cuda.get_device_properties(0).multi_processor_count * 1.965e9 / 1e12   # float32 FMA pipe
     design = args.design
-    make_config = {"givelix": givelix_config, "fororax": fororax_config, "tufevik": tufevik_config}[design]
-    rooflines = {"givelix": design_rooflines, "fororax": fororax_rooflines, "tufevik": tufevik_rooflines}[design]
+    make_config = {"givelix": givelix_config, "fororax": fororax_config, "tufevik": tufevik_config,
+                   "sebudra": sebudra_config}[design]
+    rooflines = {"givelix": design_rooflines, "fororax": fororax_rooflines, "tufevik": tufevik_rooflines,
+                 "sebudra": sebudra_rooflines}[design]
+    # designs that are set beside another model than Qwen2 as well: (label, config maker)
+    beside = {"sebudra": [("tufevik_equal_size", tufevik_config)]}.get(design, [])
     batch, out = args.batch, {"design": design, "peaks": dict(peak, fp32_fma_tflops=round(fma_tflops, 1)), "sizes": {}}
     names = [args.design_size] if args.design_size else list(DESIGN_SIZES[design])
     with ClockSampler() as clocks:
@@ -659,7 +694,8 @@ def run_design(args) -> dict:
             qwen = dict(QWEN25_1P5B, vocab_size=32768, hidden_size=shape["width"], intermediate_size=shape["ff"],
                         num_hidden_layers=6, num_attention_heads=shape["heads"], num_key_value_heads=max(2, shape["heads"] // 8))
             entry = {}
-            for label, config in ((design, make_config(**shape)), ("qwen2_equal_size", qwen)):
+            models = [(design, make_config(**shape))] + [(label, make(**shape)) for label, make in beside]
+            for label, config in models + [("qwen2_equal_size", qwen)]:
                 model = build_from_config(config, parse_dtype("bfloat16"))
                 prefill_ms = time_prefill(model)
                 decode_ms, _, _, _ = time_decode(model, batch, args.steps, max(args.warmup, 3), repeats=3)
@@ -882,6 +918,104 @@ def tufevik_rooflines(shape: dict, entry: dict, batch: int, peak: dict, fma_tflo
     out["decode"]["qwen2 attention (mma.sync, split keys)"] = frac(
         q["decode_kernels"], "attn_", 6, kv_bytes, 4 * batch * tokens * heads * 128, tensor)
     out["decode"]["qwen2 add_rmsnorm"] = frac(q["decode_kernels"], "add_rmsnorm", 13, batch * width * (4 * 2 + 4 + 2), 0, fma)
+    return out
+
+
+def sebudra_rooflines(shape: dict, entry: dict, batch: int, peak: dict, fma_tflops: float) -> dict:
+    """As :func:`design_rooflines`, for Sebudra beside Tufevik (the closest existing model) at equal size: every kind of
+    kernel that the two designs do not share, each against the slower of the bytes it must move and the operations it
+    must do (scans and row-wise kernels against the float32 FMA pipe, attention against the measured bfloat16 tensor
+    throughput)."""
+    heads, width, tokens = shape["heads"], shape["width"], PROMPT
+    kv_heads = max(2, heads // 8)
+    config = sebudra_config(**shape)
+    left, right = config["layers"][0]["mixer"]["left"], config["layers"][0]["mixer"]["right"]
+    memory, mixture = config["layers"][2]["mixer"], config["layers"][1]["mlp"]
+    window, ssm_heads, states, ssm_vdim = left["mask"]["size"], right["heads"], right["state"], right["vdim"]
+    inner, groups = ssm_heads * ssm_vdim, right["groups"]
+    conv_channels = inner + 2 * groups * states
+    gla_heads, gla_dim, gla_vdim = memory["heads"], memory["dim"], memory["vdim"]
+    experts, top, expert_ff = mixture["router"]["experts"], mixture["router"]["top"], mixture["expert"]["ff"]
+    bandwidth, tensor, fma = peak["hbm_gbs"] * 1e9, peak["bf16_tflops"] * 1e12, fma_tflops * 1e12
+
+    def frac(kernels: dict, keys, launches_of_work: float, bytes_each: float, flops_each: float, pipe: float, without=()):
+        keys = (keys,) if isinstance(keys, str) else keys
+        found = [(name, value) for name, value in kernels.items()
+                 if any(key in name for key in keys) and not any(key in name for key in without)]
+        if not found:
+            return None
+        us = sum(value["us"] for _, value in found)
+        count = sum(value["launches"] for _, value in found)
+        bound = max(bytes_each / bandwidth, flops_each / pipe) * launches_of_work
+        return {"us": round(us, 1), "launches": count, "bound_us": round(bound * 1e6, 2), "frac": round(bound * 1e6 / us, 4)}
+
+    pairs = tokens * (tokens + 1) / 2
+    windowed_pairs = tokens * window - window * (window - 1) / 2
+    s, t = entry["sebudra"], entry["tufevik_equal_size"]
+    out = {"prefill": {}, "decode": {}}
+    channels = (heads + 2 * kv_heads) * 128
+    # Both of Sebudra's scans run in the engine's matrix-memory scan kernel: two state-space layers (state rows x head
+    # channels per head) and two channel-decay memories.
+    ssm_state, gla_state = ssm_heads * states * ssm_vdim, gla_heads * gla_dim * gla_vdim
+    scan_bytes = 2 * (tokens * (conv_channels * 2 + inner * 4)) + 2 * (tokens * gla_heads * (2 * gla_dim + 2 * gla_vdim) * 4)
+    scan_flops = 2 * tokens * ssm_state * 4 * 2 + 2 * tokens * gla_state * 4 * 2       # two passes of update and read-out
+    out["prefill"]["sebudra scans (state space + channel decay, float32 FMA)"] = frac(
+        s["prefill_kernels"], "linear_attention", 1, scan_bytes, scan_flops, fma)
+    out["prefill"]["sebudra gates, decays, gated norms in parts"] = frac(
+        s["prefill_kernels"], ("ssd_gates", "sigmoid_power", "gated_group_rmsnorm"), 1,
+        2 * tokens * (inner * (4 + 4 + 2 + 2)) + 2 * tokens * gla_heads * (gla_dim * 8 + gla_vdim * 10), 0, fma)
+    out["prefill"]["sebudra convolution of the scan's inputs"] = frac(
+        s["prefill_kernels"], ("short_conv",), 2, tokens * conv_channels * (4 + 2), 0, fma)
+    attention_flops = 2 * 4 * windowed_pairs * heads * 128 + 2 * 4 * pairs * heads * 128
+    out["prefill"]["sebudra attention (2 windowed + 2 sigmoid layers)"] = frac(
+        s["prefill_kernels"], ("attention_scored", "attn_prefill_tc"), 1, 4 * tokens * channels * 2 * 2, attention_flops, tensor)
+    out["prefill"]["sebudra head norm + rotation + page write (+ branch scale)"] = frac(
+        s["prefill_kernels"], ("head_norm_rope", "head_gate_scale"), 4, tokens * channels * (4 + 2) + tokens * heads * 128 * 4, 0, fma)
+    out["prefill"]["sebudra add_rmsnorm (a stack of two branch outputs)"] = frac(
+        s["prefill_kernels"], "add_rmsnorm", 7, tokens * width * (4 * 2 + 2 * 4 + 2), 0, fma)
+    out["prefill"]["sebudra rows of the mixture (route, place, gather, activation, combine)"] = frac(
+        s["prefill_kernels"], ("moe_",), 3, tokens * width * 2 * (1 + 2 * top) + tokens * top * expert_ff * 2 * 2 + tokens * width * 4 * 2, 0, fma)
+    out["prefill"]["tufevik scans (matrix memory + selective, float32 FMA)"] = frac(
+        t["prefill_kernels"], ("linear_attention", "selective_scan"), 1,
+        3 * tokens * heads * (128 * 3 * 4 + 129 * 4) + 3 * (tokens * width * 12 + tokens * 2 * 16 * 4),
+        3 * tokens * heads * 128 * 129 * 2 * 4 + 3 * tokens * width * 16 * 6, fma)
+    out["prefill"]["tufevik attention (3 layers)"] = frac(
+        t["prefill_kernels"], ("attention_scored", "attn_prefill_tc"), 3, tokens * channels * 2 * 2, 4 * pairs * heads * 128, tensor)
+    out["prefill"]["tufevik conv_qk_norm_rope (+ head gates)"] = frac(
+        t["prefill_kernels"], ("conv_qk_norm_rope", "head_gate_scale"), 3, tokens * channels * (4 + 2) + tokens * heads * 128 * 4, 0, fma)
+    out["prefill"]["tufevik tanh_norm"] = frac(t["prefill_kernels"], "tanh_norm", 13, tokens * width * (4 * 2 + 4 + 2), 0, fma)
+    out["prefill"]["tufevik rows of the mixture"] = frac(
+        t["prefill_kernels"], ("moe_",), 3, tokens * width * 2 * (1 + 2 * top) + tokens * top * expert_ff * 2 * 3 + tokens * width * 4 * 2, 0, fma)
+    out["prefill"] = {key: value for key, value in out["prefill"].items() if value is not None}
+    # decode step at `batch` requests over 2,048-token contexts: the states are read and written once a token
+    full_kv = batch * tokens * 2 * kv_heads * 128 * 2
+    window_kv = batch * window * 2 * kv_heads * 128 * 2
+    out["decode"]["sebudra scans (4 layers)"] = frac(
+        s["decode_kernels"], "linear_attention", 1, batch * (2 * ssm_state + 2 * gla_state) * 4 * 2,
+        batch * (2 * ssm_state + 2 * gla_state) * 4, fma)
+    out["decode"]["sebudra gates, decays, gated norms in parts, convolution"] = frac(
+        s["decode_kernels"], ("ssd_gates", "sigmoid_power", "gated_group_rmsnorm", "short_conv"), 1,
+        2 * batch * (inner * 16 + conv_channels * 4 * 5) + 2 * batch * gla_heads * (gla_dim * 8 + gla_vdim * 10), 0, fma)
+    out["decode"]["sebudra attention (2 windowed + 2 sigmoid layers, chunks + merge)"] = frac(
+        s["decode_kernels"], ("attention_scored",), 1, 2 * full_kv + 2 * window_kv,
+        2 * 4 * batch * (tokens + window) * heads * 128, tensor)
+    out["decode"]["sebudra head norm + rotation + page write (+ branch scale)"] = frac(
+        s["decode_kernels"], ("head_norm_rope", "head_gate_scale"), 4, batch * channels * 4 * 5, 0, fma)
+    out["decode"]["sebudra add_rmsnorm"] = frac(s["decode_kernels"], "add_rmsnorm", 7, batch * width * (4 * 2 + 4 * 4 + 2), 0, fma)
+    out["decode"]["sebudra rows of the mixture (route, activation)"] = frac(
+        s["decode_kernels"], ("moe_",), 3, (experts + 1) * width * 2 + batch * (experts + 1) * expert_ff * 2 * 2, 0, fma)
+    out["decode"]["tufevik scans"] = frac(
+        t["decode_kernels"], ("linear_attention", "selective_scan"), 1,
+        3 * batch * heads * 128 * 129 * 4 * 2 + 3 * (batch * width * 16 * 4 * 2),
+        3 * batch * heads * 128 * 129 * 4 + 3 * batch * width * 16 * 6, fma)
+    out["decode"]["tufevik attention (chunks + merge)"] = frac(
+        t["decode_kernels"], ("attention_scored",), 3, full_kv, 4 * batch * tokens * heads * 128, tensor)
+    out["decode"]["tufevik conv_qk_norm_rope (+ head gates)"] = frac(
+        t["decode_kernels"], ("conv_qk_norm_rope", "head_gate_scale"), 3, batch * channels * 4 * 5, 0, fma)
+    out["decode"]["tufevik tanh_norm"] = frac(t["decode_kernels"], "tanh_norm", 13, batch * width * (4 * 2 + 4 + 2), 0, fma)
+    out["decode"]["tufevik rows of the mixture (route, activation)"] = frac(
+        t["decode_kernels"], ("moe_",), 3, (experts + 1) * width * 2 + batch * experts * expert_ff * 2 * 3, 0, fma)
+    out["decode"] = {key: value for key, value in out["decode"].items() if value is not None}
     return out
 
 
@@ -1205,7 +1339,7 @@ def main() -> int:
                         help="with --only: the true float32 path instead of the serving precision")
     parser.add_argument("--quick", action="store_true", help="the headline, its points and the end-to-end number only "
                                                              "(no other model sizes, no float32 point, no kernel table)")
-    parser.add_argument("--design", choices=("givelix", "fororax", "tufevik"), default=None,
+    parser.add_argument("--design", choices=("givelix", "fororax", "tufevik", "sebudra"), default=None,
                         help="instead of the default workload: the named design at layer sizes of real models beside the "
                              "Qwen2 model of equal size (prefill and decode throughput, kernel times, rooflines)")
     parser.add_argument("--design-size", choices=tuple(sorted({name for sizes in DESIGN_SIZES.values() for name in sizes})),

@@ -10,6 +10,10 @@
 // the distance only, and a tile of 64 keys and a few rows has few distances: the block works them out once a tile into
 // a small table (a logarithm per table entry instead of one per score).
 //
+// window > 0: a row reads its last `window` keys only; key tiles before the window of the tile's first row are not
+// walked, and keys before it are not fetched (their pages may have been given back).  cap > 0: scores are capped by
+// cap * tanh(s / cap).  head_bias: no softmax, a key's weight is sigmoid(s + head_bias_h) and the sums are not divided.
+//
 // With `partials` the keys of a tile of rows are cut into chunks of 256 (counted from key 0) with a block each, which
 // leaves (sums, max, total) per row, head, value slot and chunk in the layout of attention_scored.cu; that file's
 // merge kernel adds them up (and the sink).  This is how single decoded tokens and small portions fill the GPU.
@@ -38,7 +42,7 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
                             const int* __restrict__ segment_first_pos, int num_segments, const float* __restrict__ r1,
                             const float* __restrict__ r2, const float* __restrict__ sink, int n_q, int n_kv,
                             int n_values, int page_size, float scale_log2e, int rows_per_tile, int num_pages,
-                            int max_chunks) {
+                            int max_chunks, int window, float cap, const float* __restrict__ head_bias) {
   constexpr int CHK = DK / 8, CHV = DV / 8;
   constexpr int K_BYTES = tile_bytes<DK>(BN), V_BYTES = tile_bytes<DV>(BN);
   extern __shared__ __align__(128) unsigned char smem[];
@@ -65,18 +69,20 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
   const int row_base = segment_start[seg] + r0;
   const int pos0 = segment_first_pos[seg] + r0;
   const int last_pos = pos0 + nrows - 1;
-  int tile_lo = 0, tile_hi = (last_pos + BN) / BN;         // key tiles [tile_lo, tile_hi)
+  const int first_key = window > 0 ? max(0, pos0 + 1 - window) : 0;   // the first key that any row of the tile reads
+  int tile_lo = first_key / BN, tile_hi = (last_pos + BN) / BN;         // key tiles [tile_lo, tile_hi)
   if (partials) {
-    if (chunk * CHUNK > last_pos) return;
-    tile_lo = chunk * (CHUNK / BN);
-    tile_hi = min(tile_hi, tile_lo + CHUNK / BN);
+    if (chunk * CHUNK > last_pos || (chunk + 1) * CHUNK <= first_key) return;
+    tile_lo = max(tile_lo, chunk * (CHUNK / BN));
+    tile_hi = min(tile_hi, (chunk + 1) * (CHUNK / BN));
   }
   const int* bt = block_tables + (size_t)seg * bt_stride;
   const PageMath pm(page_size);
   const int n_pages = pm.page(last_pos) + 1;
   const bool staged = n_pages <= TABLE_STAGE;
   if (staged)
-    for (int i = tid; i < n_pages; i += 128) bt_s[i] = LSE_CHECKED(bt[i], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY);
+    for (int i = tid; i < n_pages; i += 128)
+      bt_s[i] = i < pm.page(first_key) ? 0 : LSE_CHECKED(bt[i], 0, num_pages, 0, LSE_CHECK_TABLE_ENTRY);
   pdl_wait();
 
   for (int e = tid; e < BM * CHK; e += 128) {
@@ -95,7 +101,8 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     const uint32_t k_dst = kv_u32 + (uint32_t)stage * (K_BYTES + V_BYTES), v_dst = k_dst + K_BYTES;
     if (page_pieces) {
       const int j0 = kt * BN + warp * 16;
-      const int limit = j0 <= last_pos ? last_pos + 1 - j0 : 0;   // keys of the piece that exist
+      const int limit = (j0 <= last_pos && j0 + 15 >= first_key) ? last_pos + 1 - j0 : 0;   // keys of the piece that exist
+      const int skip = first_key - j0;       // keys of the piece before the window: not fetched
       size_t k_base = 0, v_base = 0;
       if (limit > 0) {
         const size_t page = (size_t)bt_s[pm.page(j0)];
@@ -105,13 +112,13 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 #pragma unroll
       for (int i = 0; i < CHK / 2; ++i) {
         const int n = lane + 32 * i, row = n / CHK, c = n % CHK;
-        const bool valid = row < limit;
+        const bool valid = row < limit && row >= skip;
         cp_async16(k_dst + padded_off<DK>(warp * 16 + row, c), kc + k_base + (valid ? row * DK + c * 8 : 0), valid);
       }
 #pragma unroll
       for (int i = 0; i < CHV / 2; ++i) {
         const int n = lane + 32 * i, row = n / CHV, c = n % CHV;
-        const bool valid = row < limit;
+        const bool valid = row < limit && row >= skip;
         cp_async16(v_dst + padded_off<DV>(warp * 16 + row, c), vc + v_base + (valid ? row * DV + c * 8 : 0), valid);
       }
       return;
@@ -121,7 +128,7 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
       const int local = is_key ? idx : idx - BN * CHK;
       const int key = is_key ? local / CHK : local / CHV, c = is_key ? local % CHK : local % CHV;
       const int j = kt * BN + key;
-      const bool valid = j <= last_pos;
+      const bool valid = j <= last_pos && j >= first_key;
       size_t slot = 0;
       if (valid) {
         const int logical = pm.page(j);
@@ -148,6 +155,10 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
   const int pos_a = pos0 + min(rla, nrows - 1), pos_b = pos0 + min(rlb, nrows - 1);
   const int head_a = kvh * group + ga, head_b = kvh * group + gb;
   const bool penalised = r1 != nullptr;
+  const bool unnormalised = head_bias != nullptr;
+  const float bias_a = unnormalised ? head_bias[head_a] * LOG2E : 0.f, bias_b = unnormalised ? head_bias[head_b] * LOG2E : 0.f;
+  const float cap2 = cap * LOG2E, two_over_cap = cap > 0.f ? 2.0f / cap : 0.f;     // the cap in base two, 2 / cap in natural units
+  const float scale_natural = scale_log2e * (1.0f / LOG2E);
   const int pen_width = BN + rows_per_tile;
   const float* pen_a = pen_s + ga * pen_width + rla + (BN - 1);   // minus the key's place in the tile
   const float* pen_b = pen_s + gb * pen_width + rlb + (BN - 1);
@@ -191,6 +202,7 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
       }
     }
     const bool diagonal = (kt + 1) * BN - 1 > pos0;   // some row of the tile ends inside these keys
+    const bool windowed = window > 0 && kt * BN <= last_pos - window;   // some row of the tile starts inside or behind them
     float mx0 = -INFINITY, mx1 = -INFINITY;
 #pragma unroll
     for (int nb = 0; nb < BN / 8; ++nb) {
@@ -200,8 +212,13 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
         const int j = kt * BN + key;
         const int pos = (e >> 1) ? pos_b : pos_a;
         float v = s[nb][e] * scale_log2e;
+        if (cap > 0.f) {    // cap * tanh(x / cap) = cap * (1 - 2 / (exp(2 x / cap) + 1)), x the natural score
+          const float t = fast_exp2(s[nb][e] * scale_natural * two_over_cap * LOG2E);
+          v = cap2 * (1.0f - __fdividef(2.0f, t + 1.0f));
+        }
         if (penalised) v -= ((e >> 1) ? pen_b : pen_a)[-key];
         if (diagonal && j > pos) v = -INFINITY;
+        if (windowed && j <= pos - window) v = -INFINITY;
         s[nb][e] = v;
       }
       mx0 = fmaxf(mx0, fmaxf(s[nb][0], s[nb][1]));
@@ -213,6 +230,17 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
     // A row that sees no key of this chunk (its position lies before it) keeps max = -inf; it is never written, and
     // its registers are kept free of NaN by taking 0 for the maximum.
+    if (unnormalised) {   // sigmoid(s + b) = 1 / (1 + 2^-(s2 + b2)); a masked key (-inf) weighs 0; nothing is rescaled
+#pragma unroll
+      for (int nb = 0; nb < BN / 8; ++nb) {
+        s[nb][0] = __fdividef(1.0f, 1.0f + fast_exp2(-(s[nb][0] + bias_a)));
+        s[nb][1] = __fdividef(1.0f, 1.0f + fast_exp2(-(s[nb][1] + bias_a)));
+        s[nb][2] = __fdividef(1.0f, 1.0f + fast_exp2(-(s[nb][2] + bias_b)));
+        s[nb][3] = __fdividef(1.0f, 1.0f + fast_exp2(-(s[nb][3] + bias_b)));
+      }
+      m0 = m1 = 0.f;
+      l0 = l1 = 0.25f;     // four lanes add theirs: the total that the merge reads is one, and is not used
+    } else {
     const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
     const float base0 = mn0 == -INFINITY ? 0.f : mn0, base1 = mn1 == -INFINITY ? 0.f : mn1;
     const float c0 = fast_exp2(m0 - base0), c1 = fast_exp2(m1 - base1);
@@ -229,6 +257,7 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     l1 = l1 * c1 + sum1;
 #pragma unroll
     for (int i = 0; i < DV / 8; ++i) { acc[i][0] *= c0; acc[i][1] *= c0; acc[i][2] *= c1; acc[i][3] *= c1; }
+    }
     {
       const int mi = lane >> 3, key = (lane & 7) + (mi & 1) * 8;
 #pragma unroll
@@ -252,7 +281,8 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
 
   if (partials) {   // unnormalised sums, the maximum in natural units, the total: for the merge kernel
     constexpr float LN2 = 0.6931471805599453f;
-    const bool write_a = rla < nrows && chunk * CHUNK <= pos_a, write_b = rlb < nrows && chunk * CHUNK <= pos_b;
+    const bool write_a = rla < nrows && chunk * CHUNK <= pos_a && (window <= 0 || (chunk + 1) * CHUNK > pos_a + 1 - window);
+    const bool write_b = rlb < nrows && chunk * CHUNK <= pos_b && (window <= 0 || (chunk + 1) * CHUNK > pos_b + 1 - window);
     float* dst_a = partials + ((((size_t)(row_base + rla) * n_q + head_a) * n_values + value_slot) * max_chunks + chunk) * (DV + 2);
     float* dst_b = partials + ((((size_t)(row_base + rlb) * n_q + head_b) * n_values + value_slot) * max_chunks + chunk) * (DV + 2);
 #pragma unroll
@@ -275,7 +305,7 @@ attention_scored_mma_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bflo
     l0 = l0 * w0 + fast_exp2(sa - na);
     l1 = l1 * w1 + fast_exp2(sb - nb);
   }
-  const float inv0 = w0 / l0, inv1 = w1 / l1;
+  const float inv0 = unnormalised ? 1.f : w0 / l0, inv1 = unnormalised ? 1.f : w1 / l1;
 #pragma unroll
   for (int i = 0; i < DV / 8; ++i) {
     const int d = i * 8 + (lane & 3) * 2;
@@ -296,7 +326,8 @@ template <int D>
 int launch_scored_mma(const void* q, const void* kc, const void* vc, void* out, int out_is_f32, float* partials,
                       const int* block_tables, int bt_stride, const int* segment_start, const int* segment_first_pos,
                       int num_segments, const float* r1, const float* r2, const float* sink, int tokens, int n_q, int n_kv,
-                      int n_values, int page_size, float scale, int num_pages, int max_chunks, cudaStream_t stream) {
+                      int n_values, int page_size, float scale, int num_pages, int max_chunks, int window, float cap,
+                      const float* head_bias, cudaStream_t stream) {
   const int group = n_q / n_kv;
   const int rows_per_tile = BM / group;
   const size_t tiles_bytes = (size_t)tile_bytes<D>(BM) + 2 * (size_t)(tile_bytes<D>(BN) + tile_bytes<D>(BN));
@@ -315,7 +346,8 @@ int launch_scored_mma(const void* q, const void* kc, const void* vc, void* out, 
   lse_launch(attention_scored_mma_kernel<D, D>, grid, 128, smem, stream, (const __nv_bfloat16*)q, (const __nv_bfloat16*)kc,
              (const __nv_bfloat16*)vc, out_is_f32 ? (__nv_bfloat16*)nullptr : (__nv_bfloat16*)out,
              out_is_f32 ? (float*)out : (float*)nullptr, partials, block_tables, bt_stride, segment_start, segment_first_pos,
-             num_segments, r1, r2, sink, n_q, n_kv, n_values, page_size, scale * LOG2E, rows_per_tile, num_pages, max_chunks);
+             num_segments, r1, r2, sink, n_q, n_kv, n_values, page_size, scale * LOG2E, rows_per_tile, num_pages, max_chunks,
+             window, cap, head_bias);
   return (int)cudaGetLastError();
 }
 }  // namespace
@@ -330,19 +362,22 @@ extern "C" int lse_attention_scored_mma_supported(int dk, int dv, int n_q, int n
 // The arguments of lse_attention_scored, with the step's rows described by segments (segment_start int32 [S + 1],
 // segment_first_pos int32 [S]) instead of row by row.  Without `partials` the result goes to `out` (bfloat16, or
 // float32 when out_f32); with them the caller runs lse_attention_scored_merge afterwards.
-extern "C" int lse_attention_scored_mma(const void* q, const void* k_cache, const void* v_cache, void* out, int out_f32,
-                                        const int* block_tables, int bt_stride, const int* segment_start,
-                                        const int* segment_first_pos, int num_segments, const float* r1, const float* r2,
-                                        const float* sink, int tokens, int n_q, int n_kv, int dk, int dv, int cross,
-                                        int page_size, float scale, int num_pages, float* partials, int max_chunks,
-                                        cudaStream_t stream) {
+extern "C" int lse_attention_scored_mma_windowed(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                                 int out_f32, const int* block_tables, int bt_stride,
+                                                 const int* segment_start, const int* segment_first_pos, int num_segments,
+                                                 const float* r1, const float* r2, const float* sink, int tokens, int n_q,
+                                                 int n_kv, int dk, int dv, int cross, int page_size, float scale,
+                                                 int num_pages, float* partials, int max_chunks, int window, float cap,
+                                                 const float* head_bias, cudaStream_t stream) {
   if (tokens <= 0) return 0;
+  if (head_bias && sink) return LSE_ERR_BAD_ARGUMENT;
   if (!lse_attention_scored_mma_supported(dk, dv, n_q, n_kv) || page_size <= 0 || (!r1) != (!r2)) return LSE_ERR_BAD_ARGUMENT;
   if (partials && (max_chunks <= 0 || (long long)max_chunks * CHUNK < (long long)bt_stride * page_size))
     return LSE_ERR_BAD_ARGUMENT;
   const int n_values = cross ? n_kv : 1;
 #define LSE_SCORED_MMA_ARGS q, k_cache, v_cache, out, out_f32, partials, block_tables, bt_stride, segment_start, \
-  segment_first_pos, num_segments, r1, r2, sink, tokens, n_q, n_kv, n_values, page_size, scale, num_pages, max_chunks, stream
+  segment_first_pos, num_segments, r1, r2, sink, tokens, n_q, n_kv, n_values, page_size, scale, num_pages, max_chunks, \
+  window, cap, head_bias, stream
   switch (dk) {
     case 32: return launch_scored_mma<32>(LSE_SCORED_MMA_ARGS);
     case 48: return launch_scored_mma<48>(LSE_SCORED_MMA_ARGS);
@@ -351,4 +386,15 @@ extern "C" int lse_attention_scored_mma(const void* q, const void* k_cache, cons
     default: return launch_scored_mma<128>(LSE_SCORED_MMA_ARGS);
   }
 #undef LSE_SCORED_MMA_ARGS
+}
+
+extern "C" int lse_attention_scored_mma(const void* q, const void* k_cache, const void* v_cache, void* out, int out_f32,
+                                        const int* block_tables, int bt_stride, const int* segment_start,
+                                        const int* segment_first_pos, int num_segments, const float* r1, const float* r2,
+                                        const float* sink, int tokens, int n_q, int n_kv, int dk, int dv, int cross,
+                                        int page_size, float scale, int num_pages, float* partials, int max_chunks,
+                                        cudaStream_t stream) {
+  return lse_attention_scored_mma_windowed(q, k_cache, v_cache, out, out_f32, block_tables, bt_stride, segment_start,
+                                           segment_first_pos, num_segments, r1, r2, sink, tokens, n_q, n_kv, dk, dv, cross,
+                                           page_size, scale, num_pages, partials, max_chunks, 0, 0.f, nullptr, stream);
 }

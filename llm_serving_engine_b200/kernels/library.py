@@ -159,6 +159,11 @@ _SIGNATURES = {
                                 c_float, c_float, c_int, c_int, c_void_p, c_void_p],
     "lse_moe_route_sigmoid": [c_void_p, c_int, c_longlong, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                               c_int, c_int, c_int, c_int, c_int, c_float, c_void_p],
+    "lse_attention_scored_mma_windowed": [c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p,
+                                          c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int, c_int, c_int, c_int, c_int,
+                                          c_float, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p],
+    "lse_attention_scored_merge_windowed": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
+                                            c_int, c_int, c_int, c_int, c_int, c_void_p],
     "lse_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "lse_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p],
@@ -199,7 +204,8 @@ def register_signatures(signatures: dict) -> None:
 
 
 CHECK_READERS = ("lse_check_elementwise", "lse_check_attention_generic", "lse_check_attention_mma", "lse_check_attention_tc",
-                 "lse_check_residual_streams", "lse_check_linear_attention", "lse_check_attention_latent",
+                 "lse_check_residual_streams", "lse_check_linear_attention", "lse_check_linear_attention_gated",
+                 "lse_check_linear_attention_vector", "lse_check_attention_latent",
                  "lse_check_attention_latent_mma", "lse_check_rowwise_postnorm", "lse_check_attention_scored",
                  "lse_check_attention_scored_mma", "lse_check_mlstm", "lse_check_short_conv", "lse_check_selective_scan")
 CHECK_KINDS = {1: "token id", 2: "cache slot", 3: "block-table entry", 4: "segment number", 5: "row index"}

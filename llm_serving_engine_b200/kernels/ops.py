@@ -853,7 +853,6 @@ def attention_scored(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
     weights are not normalised over the keys."""
     _need_cuda(q, k_cache, v_cache, out, block_tables, segment_of_token, positions, r1, r2, sink, segment_start,
                segment_first_position, head_bias)
-    changed = window > 0 or cap > 0.0 or head_bias is not None
     tokens, n_q, dk = q.shape
     n_kv, page_size, dv = k_cache.shape[1], k_cache.shape[2], v_cache.shape[3]
     n_values = n_kv if cross else 1
@@ -873,21 +872,21 @@ def attention_scored(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tens
         chunk = int(lib.lse_attention_scored_chunk())
         max_chunks = max(1, -(-(block_tables.stride(0) * page_size) // chunk))
         partials = torch.empty(tokens * n_q * n_values * max_chunks * (dv + 2), dtype=torch.float32, device=q.device)
-    if (tensor_cores and not changed and segment_start is not None and segment_first_position is not None
+    if (tensor_cores and segment_start is not None and segment_first_position is not None
             and attention_scored_mma_supported(dk, dv, n_q, n_kv, q.dtype)):
         segments = segment_first_position.shape[0]
         assert segment_start.dtype == torch.int32 and segment_start.shape[0] == segments + 1 and segments == block_tables.shape[0]
-        check(lib.lse_attention_scored_mma(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
-                                           int(out.dtype == torch.float32), block_tables.data_ptr(), block_tables.stride(0),
-                                           segment_start.data_ptr(), segment_first_position.data_ptr(), segments, _ptr(r1),
-                                           _ptr(r2), _ptr(sink), tokens, n_q, n_kv, dk, dv, int(cross), page_size,
-                                           float(scale), k_cache.shape[0], _ptr(partials), max_chunks, _stream()),
-              "attention_scored_mma")
+        check(lib.lse_attention_scored_mma_windowed(
+            q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), int(out.dtype == torch.float32),
+            block_tables.data_ptr(), block_tables.stride(0), segment_start.data_ptr(), segment_first_position.data_ptr(),
+            segments, _ptr(r1), _ptr(r2), _ptr(sink), tokens, n_q, n_kv, dk, dv, int(cross), page_size, float(scale),
+            k_cache.shape[0], _ptr(partials), max_chunks, int(window), float(cap), _ptr(head_bias), _stream()),
+            "attention_scored_mma")
         if partials is not None:
-            check(lib.lse_attention_scored_merge(partials.data_ptr(), out.data_ptr(), dtype_code(out.dtype),
-                                                 segment_of_token.data_ptr(), positions.data_ptr(), _ptr(sink), tokens, n_q,
-                                                 n_values, dv, max_chunks, block_tables.shape[0], _stream()),
-                  "attention_scored_merge")
+            check(lib.lse_attention_scored_merge_windowed(
+                partials.data_ptr(), out.data_ptr(), dtype_code(out.dtype), segment_of_token.data_ptr(),
+                positions.data_ptr(), _ptr(sink), tokens, n_q, n_values, dv, max_chunks, block_tables.shape[0],
+                int(window), int(head_bias is not None), _stream()), "attention_scored_merge")
         return out
     check(lib.lse_attention_scored_windowed(
         q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(), dtype_code(q.dtype),

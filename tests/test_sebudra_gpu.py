@@ -354,14 +354,20 @@ def _plain_attention(q, k, v, scale, window=0, cap=0.0, head_bias=None):
     return plain.apply_weights(weights, v.double()).view(total, q.shape[1], v.shape[2])
 
 
+# head sizes that the general kernel takes (keys and values of different sizes) and that the tensor-core kernel takes in bfloat16
+_HEAD_SIZES = [(4, 2, 24, 40), (4, 2, 64, 64), (6, 2, 48, 48), (8, 1, 128, 128)]
+
+
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("sizes", _HEAD_SIZES)
 @pytest.mark.parametrize("window", [1, 7, 40, 256, 300])
-def test_a_window_ends_where_it_should(dtype, window):
+def test_a_window_ends_where_it_should(dtype, window, sizes):
     """One key far stronger than the others sits just inside and just outside the last row's window (and the rows before
     it see it or not by their own windows), at page and chunk borders; the rows come whole, as a prompt and a single
     token, and in portions of two."""
     torch.manual_seed(11)
-    n_q, n_kv, dk, dv, context, page, scale = 4, 2, 24, 40, 330, 16, 0.3
+    (n_q, n_kv, dk, dv), context, page = sizes, 330, 16
+    scale = 1.5 / dk ** 0.5
     for back in (window - 1, window, window + 1, 0):       # the strong key's distance from the last row
         special = context - 1 - back
         if special < 0:
@@ -382,12 +388,14 @@ def test_a_window_ends_where_it_should(dtype, window):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-def test_sigmoid_weights_are_not_normalised_and_find_a_far_key(dtype):
+@pytest.mark.parametrize("sizes", [(6, 2, 16, 24), (6, 2, 64, 64), (6, 3, 32, 32), (6, 1, 128, 128)])
+def test_sigmoid_weights_are_not_normalised_and_find_a_far_key(dtype, sizes):
     """Weights sigmoid(capped score + a number per head): the output grows with the number of keys (a softmax's would
     not), the cap bounds what one key can weigh, and one far key with a large score and a large value shows at the
     borders of pages, tiles and chunks, in prompts, single tokens and portions of two."""
     torch.manual_seed(12)
-    n_q, n_kv, dk, dv, context, page, scale, cap = 6, 2, 16, 24, 300, 16, 0.5, 4.0
+    (n_q, n_kv, dk, dv), context, page, cap = sizes, 300, 16, 4.0
+    scale = 2.0 / dk ** 0.5
     head_bias = torch.tensor([-6.0, -2.0, 0.0, 1.0, -4.0, -3.0])
     for special in (0, 1, 15, 16, 17, 31, 32, 255, 256, 257, 297, 298):
         q, k, v = (torch.randn(context, n, d).to(dtype).float() for n, d in ((n_q, dk), (n_kv, dk), (n_kv, dv)))
@@ -395,7 +403,8 @@ def test_sigmoid_weights_are_not_normalised_and_find_a_far_key(dtype):
         v[special, 0] = 9.0
         want = _plain_attention(q, k, v, scale, cap=cap, head_bias=head_bias)
         assert float(want[-1, 0].mean()) > 0.1 * 9.0 * float(torch.sigmoid(torch.tensor(cap - 6.0)))
-        assert float(want[-1, 3].abs().mean()) > 2.0 * float(want[9, 3].abs().mean())     # more keys, larger sums
+        total = _plain_attention(q, k, torch.ones_like(v), scale, cap=cap, head_bias=head_bias)      # the weights' sums
+        assert float(total[-1, 3].mean()) > 100.0 > 12.0 > float(total[9, 3].mean()) > 3.0      # a softmax's would be one
         for cuts in ([(0, context)], [(0, context - 1), (context - 1, 1)], _cuts(context, (2,)) if special in (16, 257) else None):
             if cuts is None:
                 continue

@@ -94,7 +94,10 @@ constexpr size_t attn_tc_smem() {
 // joins the softmax's denominator.  n_values > 1: blockIdx.y is the key/value head whose VALUES the block applies its
 // head's weights to (the keys are always the head's own), and the output has a slot per value head:
 // out[((row * n_q + head) * n_values + slot) * D].
-template <int D, bool PEN>
+// MODE 2 (SIG): no softmax.  A key's weight is sigmoid(c(s) + b_h), with c the cap `cap * tanh(s / cap)` (cap <= 0: none) and
+// b_h a number per head (passed in r1); the weights are not normalised: the maximum in use stays zero, nothing is ever
+// rescaled, and the sums are not divided at the end.
+template <int D, int MODE>
 __global__ void __launch_bounds__(THREADS, 1)
 attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_k,
                        const __grid_constant__ CUtensorMap map_v, __nv_bfloat16* __restrict__ out,
@@ -102,7 +105,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
                        const int* __restrict__ segment_first_pos, int num_segments, int n_q, int n_kv, int page_size,
                        float scale_log2e, int num_pages, int skip_single, int parts, float* __restrict__ scratch,
                        int* __restrict__ counters, const float* __restrict__ r1, const float* __restrict__ r2,
-                       const float* __restrict__ sink, int n_values) {
+                       const float* __restrict__ sink, int n_values, float cap) {
+  constexpr bool PEN = MODE == 1, SIG = MODE == 2;
   constexpr int HALVES = D / 64;
   constexpr uint32_t Q_BYTES = HALVES * HALF_BYTES, KV_BYTES = HALVES * HALF_BYTES, P_BYTES = 2 * HALF_BYTES;
   constexpr uint32_t GROUP_BYTES = HALVES * 1024;   // 8 keys (or values) in a stage: 8 rows x 128 bytes for every 64 columns
@@ -281,6 +285,8 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     unsigned char* prow = gbase + (p_s - base) + g * P_BYTES + row * 128;
     float m_used = -INFINITY, m_seen = -INFINITY, l = 0.f;   // the maximum that O and l are relative to; the largest score seen
     const float pen1 = PEN ? r1[head] : 0.f, pen2 = PEN ? r2[head] : 0.f;
+    const float bias2 = SIG ? r1[head] * LOG2E : 0.f;                  // the head's number, in base two
+    const float cap2 = cap * LOG2E, cap_step = cap > 0.f ? scale_log2e * 2.0f / cap : 0.f;   // 2^(s cap_step) = exp(2 x / cap)
     // the penalty of key `key` for this thread's row, in base two (hidden keys, beyond the row's position, get none)
     // (Reading it from a table of all distances worked out ahead was measured no faster: what the penalty costs is
     // the softmax threads' issue slots and registers, not the logarithm.)
@@ -306,7 +312,9 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
       const bool first = j < GROUPS;                 // this group's first tile
       bool rescale = false;
       float alpha = 1.f;
-      if (first) {
+      if (SIG) {
+        m_used = m_seen = 0.f;      // the weights are taken as they are
+      } else if (first) {
         // the row maximum of the first tile is found before anything is exponentiated
         float mx = -INFINITY;
 #pragma unroll
@@ -380,6 +388,19 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
             float s0 = __uint_as_float(s[2 * i]), s1 = __uint_as_float(s[2 * i + 1]);
             float s2 = __uint_as_float(s[2 * i + 2]), s3 = __uint_as_float(s[2 * i + 3]);
             float p0, p1, p2, p3;
+            if (SIG) {   // capped, the head's number added, through the sigmoid; a hidden key (-inf) weighs nothing
+              auto weigh = [&](float raw) {
+                float x2 = raw * scale_log2e;
+                if (cap > 0.f) x2 = cap2 * (1.0f - __fdividef(2.0f, exp2_fast(raw * cap_step) + 1.0f));
+                const float w = __fdividef(1.0f, 1.0f + exp2_fast(-(x2 + bias2)));
+                return raw == -INFINITY ? 0.f : w;
+              };
+              p0 = weigh(s0); p1 = weigh(s1); p2 = weigh(s2); p3 = weigh(s3);
+              sum += (p0 + p1) + (p2 + p3);
+              pk[i] = pack_bf16(p0, p1);
+              pk[i + 1] = pack_bf16(p2, p3);
+              continue;
+            }
             if (PEN) {   // scaled and penalised first: the maximum is taken over what is exponentiated
               const float ahead = ahead_of_chunk - (float)(2 * i);
               s0 = fmaf(s0, scale_log2e, -penalty(ahead)); s1 = fmaf(s1, scale_log2e, -penalty(ahead - 1.0f));
@@ -464,7 +485,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
     const bool shared = sharing > 1;
     float inv = 1.0f;
     if (!shared) {
-      inv = 1.0f / l_all;
+      inv = SIG ? 1.0f : 1.0f / l_all;
       if (sink) {   // exp(sink) joins the sum; the outputs are rescaled when the sink is the new maximum
         const float sink2 = sink[head] * LOG2E;
         const float m_fin = fmaxf(m_all, sink2);
@@ -557,7 +578,7 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
           if (p < sharing) sum = fmaf(__ldcg(parts_base + (size_t)p * PART_FLOATS + BM * D + BM + row), weight[p], sum);
         }
         if (sink) sum += exp2_fast(sink2 - m_tile);
-        const float inv_sum = 1.0f / sum;
+        const float inv_sum = SIG ? 1.0f : 1.0f / sum;
         if (row < nrows) {
 #pragma unroll 2
           for (int c = 0; c < OD; c += 8) {
@@ -593,16 +614,16 @@ attn_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_c
 #endif
 }
 
-template <int D, bool PEN>
+template <int D, int MODE>
 int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, const int* block_tables, int bt_stride,
                       const int* segment_start, const int* segment_first_pos, int num_segments, int tokens,
                       long long num_pages, int n_q, int n_kv, int page_size, float scale, int skip_single,
                       int max_portions, float* scratch, int* counters, long long scratch_slots, const float* r1,
-                      const float* r2, const float* sink, int n_values, cudaStream_t stream) {
+                      const float* r2, const float* sink, int n_values, cudaStream_t stream, float cap = 0.f) {
   const size_t smem = attn_tc_smem<D>();
   static bool configured = false;
   if (!configured) {
-    cudaError_t err = cudaFuncSetAttribute(attn_prefill_tc_kernel<D, PEN>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+    cudaError_t err = cudaFuncSetAttribute(attn_prefill_tc_kernel<D, MODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     if (err != cudaSuccess) return (int)err;
     configured = true;
   }
@@ -631,10 +652,10 @@ int launch_prefill_tc(const void* q, const void* kc, const void* vc, void* out, 
   }
   if (n_values > 65535) return LSE_ERR_TOO_LARGE;
   dim3 grid((unsigned)(blocks * parts), (unsigned)n_values);
-  cudaError_t err = lse_launch(attn_prefill_tc_kernel<D, PEN>, grid, THREADS, smem, stream, map_q, map_k, map_v,
+  cudaError_t err = lse_launch(attn_prefill_tc_kernel<D, MODE>, grid, THREADS, smem, stream, map_q, map_k, map_v,
                                (__nv_bfloat16*)out, block_tables, bt_stride, segment_start, segment_first_pos,
                                num_segments, n_q, n_kv, page_size, scale * LOG2E, (int)num_pages, skip_single, parts,
-                               scratch, counters, r1, r2, sink, n_values);
+                               scratch, counters, r1, r2, sink, n_values, cap);
   if (err != cudaSuccess) return (int)err;
   return (int)cudaGetLastError();
 }
@@ -692,10 +713,10 @@ extern "C" int lse_paged_attention_prefill_tc(const void* q, const void* k_cache
       (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15))
     return LSE_ERR_BAD_ARGUMENT;
   if (head_dim == 128)
-    return launch_prefill_tc<128, false>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
+    return launch_prefill_tc<128, 0>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
                                          num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions,
                                          scratch, counters, scratch_slots, nullptr, nullptr, nullptr, 1, stream);
-  return launch_prefill_tc<64, false>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
+  return launch_prefill_tc<64, 0>(q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos,
                                       num_segments, tokens, num_pages, n_q, n_kv, page_size, scale, skip_single, max_portions,
                                       scratch, counters, scratch_slots, nullptr, nullptr, nullptr, 1, stream);
 }
@@ -717,7 +738,26 @@ extern "C" int lse_attention_scored_tc(const void* q, const void* k_cache, const
   const int n_values = cross ? n_kv : 1;
 #define LSE_SCORED_TC_ARGS q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos, num_segments, \
   tokens, num_pages, n_q, n_kv, page_size, scale, 0, 0, scratch, counters, scratch_slots, r1, r2, sink, n_values, stream
-  if (head_dim == 128) return r1 ? launch_prefill_tc<128, true>(LSE_SCORED_TC_ARGS) : launch_prefill_tc<128, false>(LSE_SCORED_TC_ARGS);
-  return r1 ? launch_prefill_tc<64, true>(LSE_SCORED_TC_ARGS) : launch_prefill_tc<64, false>(LSE_SCORED_TC_ARGS);
+  if (head_dim == 128) return r1 ? launch_prefill_tc<128, 1>(LSE_SCORED_TC_ARGS) : launch_prefill_tc<128, 0>(LSE_SCORED_TC_ARGS);
+  return r1 ? launch_prefill_tc<64, 1>(LSE_SCORED_TC_ARGS) : launch_prefill_tc<64, 0>(LSE_SCORED_TC_ARGS);
 #undef LSE_SCORED_TC_ARGS
+}
+
+// The same kernel without a softmax: a key's weight is sigmoid(cap * tanh(s / cap) + head_bias_h) (cap <= 0: no cap), not
+// normalised over the keys; head_bias float32 [n_q]; out [tokens, n_q, D].
+extern "C" int lse_attention_sigmoid_tc(const void* q, const void* k_cache, const void* v_cache, void* out,
+                                        const int* block_tables, int bt_stride, const int* segment_start,
+                                        const int* segment_first_pos, int num_segments, int tokens, long long num_pages,
+                                        int n_q, int n_kv, int head_dim, int page_size, float scale, const float* head_bias,
+                                        float cap, float* scratch, int* counters, long long scratch_slots,
+                                        cudaStream_t stream) {
+  if (tokens <= 0 || num_segments <= 0) return 0;
+  if (!lse_attention_tc_supported(head_dim, n_q, n_kv, page_size) || num_pages <= 0 || !(scale > 0.f) || !head_bias ||
+      (((uintptr_t)q | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)out) & 15))
+    return LSE_ERR_BAD_ARGUMENT;
+#define LSE_SIGMOID_TC_ARGS q, k_cache, v_cache, out, block_tables, bt_stride, segment_start, segment_first_pos, num_segments, \
+  tokens, num_pages, n_q, n_kv, page_size, scale, 0, 0, scratch, counters, scratch_slots, head_bias, nullptr, nullptr, 1, stream, cap
+  if (head_dim == 128) return launch_prefill_tc<128, 2>(LSE_SIGMOID_TC_ARGS);
+  return launch_prefill_tc<64, 2>(LSE_SIGMOID_TC_ARGS);
+#undef LSE_SIGMOID_TC_ARGS
 }

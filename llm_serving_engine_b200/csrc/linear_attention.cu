@@ -77,7 +77,9 @@ sigmoid_power_kernel(const TD* __restrict__ proj, int n_partials, long long part
 //   a_i = o_i + skip[i / head_width] * x_i          (skip null: a = o;  x: columns x_off .. of `xsrc`)
 //   gate_first:  b = a * act(g);  out = b / rms(b) * weight[i % weight_len] * scale
 //   else:                         out = a / rms(a) * weight[i % weight_len] * act(g) * scale
-// with act the SiLU (gate_act 1) or the sigmoid (0); g: columns g_off .. of proj.  A warp owns a part at a time.
+// with act the SiLU (gate_act 1) or the sigmoid (0); g: columns g_off .. of proj.  A block owns one part of one row
+// (grid: rows x parts); a thread keeps up to GGN_KEPT of the part's values (and gates) between the sum and the write.
+constexpr int GGN_KEPT = 8;
 template <typename TD, typename TO>
 __global__ void __launch_bounds__(256)
 gated_group_rmsnorm_kernel(const float* __restrict__ o, const TD* __restrict__ proj, int n_partials,
@@ -86,12 +88,12 @@ gated_group_rmsnorm_kernel(const float* __restrict__ o, const TD* __restrict__ p
                            const float* __restrict__ weight, int weight_len, TO* __restrict__ out, long long out_ld,
                            int n, int groups, float eps, float scale, int gate_first, int gate_act,
                            const int* __restrict__ segment_of_token) {
+  __shared__ float scratch[32];
   pdl_launch_dependents();
   pdl_wait();
-  const int t = blockIdx.x;
+  const int t = blockIdx.x, part = blockIdx.y;
   if (segment_of_token && segment_of_token[t] < 0) return;
-  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = blockDim.x >> 5;
-  const int width = n / groups;
+  const int width = n / groups, lo = part * width;
   const float* row = o + (size_t)t * n;
   const TD* g = proj + (size_t)t * ld + g_off;
   auto gate = [&](int i) {
@@ -99,21 +101,42 @@ gated_group_rmsnorm_kernel(const float* __restrict__ o, const TD* __restrict__ p
     const float sg = 1.f / (1.f + expf(-z));
     return gate_act == 1 ? z * sg : sg;
   };
-  auto value = [&](int i) {
+  auto plain = [&](int i) {
     float a = row[i];
     if (skip) a = fmaf(skip[i / head_width], to_f32<TO>(xsrc[(size_t)t * x_ld + x_off + i]), a);
-    return gate_first ? a * gate(i) : a;
+    return a;
   };
-  for (int part = warp; part < groups; part += warps) {
-    const int lo = part * width;
-    float sq = 0.f;
-    for (int i = lo + lane; i < lo + width; i += 32) { const float v = value(i); sq = fmaf(v, v, sq); }
-    const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
-    for (int i = lo + lane; i < lo + width; i += 32) {
-      float y = (value(i) * inv) * weight[i % weight_len];
-      if (!gate_first) y *= gate(i);
+  float kept[GGN_KEPT], gates[GGN_KEPT];
+  float sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < GGN_KEPT; ++k) {
+    const int i = lo + threadIdx.x + k * blockDim.x;
+    kept[k] = gates[k] = 0.f;
+    if (i < lo + width) {
+      gates[k] = gate(i);
+      kept[k] = gate_first ? plain(i) * gates[k] : plain(i);
+      sq = fmaf(kept[k], kept[k], sq);
+    }
+  }
+  for (int i = lo + threadIdx.x + GGN_KEPT * blockDim.x; i < lo + width; i += blockDim.x) {
+    const float v = gate_first ? plain(i) * gate(i) : plain(i);
+    sq = fmaf(v, v, sq);
+  }
+  const float inv = 1.0f / sqrtf(block_sum(sq, scratch) / (float)width + eps);
+#pragma unroll
+  for (int k = 0; k < GGN_KEPT; ++k) {
+    const int i = lo + threadIdx.x + k * blockDim.x;
+    if (i < lo + width) {
+      float y = (kept[k] * inv) * weight[i % weight_len];
+      if (!gate_first) y *= gates[k];
       out[(size_t)t * out_ld + i] = from_f32<TO>(y * scale);
     }
+  }
+  for (int i = lo + threadIdx.x + GGN_KEPT * blockDim.x; i < lo + width; i += blockDim.x) {
+    const float gi = gate(i);
+    float y = ((gate_first ? plain(i) * gi : plain(i)) * inv) * weight[i % weight_len];
+    if (!gate_first) y *= gi;
+    out[(size_t)t * out_ld + i] = from_f32<TO>(y * scale);
   }
 }
 }  // namespace
@@ -195,9 +218,12 @@ extern "C" int lse_gated_group_rmsnorm(const float* o, const void* proj, int pro
   if (tokens <= 0) return 0;
   if (n <= 0 || groups <= 0 || n % groups || weight_len <= 0 || n_partials < 1 || (skip && (!xsrc || head_width <= 0)))
     return LSE_ERR_BAD_ARGUMENT;
-  const int threads = groups >= 8 ? 256 : (groups >= 4 ? 128 : 32 * groups);
+  if (groups > 65535) return LSE_ERR_TOO_LARGE;
+  const int width = n / groups;
+  const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : (width > 32 ? 64 : 32));
+  const dim3 grid(tokens, groups);
 #define LSE_GGN_CASE(TD, TO)                                                                                         \
-  lse_launch(gated_group_rmsnorm_kernel<TD, TO>, tokens, threads, 0, stream, o, (const TD*)proj, n_partials,          \
+  lse_launch(gated_group_rmsnorm_kernel<TD, TO>, grid, threads, 0, stream, o, (const TD*)proj, n_partials,            \
              partial_stride, ld, g_off, (const TO*)xsrc, x_ld, x_off, skip, head_width, weight, weight_len, (TO*)out, \
              out_ld, n, groups, eps, scale, gate_first, gate_act, segment_of_token);
   const bool d32 = proj_dtype == LSE_DTYPE_F32, o32 = out_dtype == LSE_DTYPE_F32;

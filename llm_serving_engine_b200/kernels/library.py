@@ -164,6 +164,9 @@ _SIGNATURES = {
                                           c_float, c_int, c_void_p, c_int, c_int, c_float, c_void_p, c_void_p],
     "lse_attention_scored_merge_windowed": [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_int, c_int, c_int,
                                             c_int, c_int, c_int, c_int, c_int, c_void_p],
+    "lse_attention_sigmoid_tc": [c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, c_int,
+                                 c_longlong, c_int, c_int, c_int, c_int, c_float, c_void_p, c_float, c_void_p, c_void_p,
+                                 c_longlong, c_void_p],
     "lse_argmax": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p],
     "lse_sample": [c_void_p, c_longlong, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
                    c_void_p, c_void_p, c_void_p],

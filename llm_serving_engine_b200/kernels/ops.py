@@ -931,6 +931,31 @@ def attention_scored_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.T
     return out
 
 
+def attention_sigmoid_tc(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, out: torch.Tensor,
+                         block_tables: torch.Tensor, segment_start: torch.Tensor, segment_first_position: torch.Tensor,
+                         scale: float, head_bias: torch.Tensor, cap: float = 0.0) -> torch.Tensor:
+    """:func:`attention_scored` with ``head_bias`` (weights sigmoid(capped score + head_bias_h), not normalised over the
+    keys) for prompt portions on the 5th-generation tensor cores: the shapes of :func:`attention_scored_tc`; out
+    [T, n_q, dv] bfloat16.  Every request of the step is worked on in tiles of 128 rows."""
+    _need_cuda(q, k_cache, v_cache, out, block_tables, segment_start, segment_first_position, head_bias)
+    tokens, n_q, head_dim = q.shape
+    pages, n_kv, page_size = k_cache.shape[0], k_cache.shape[1], k_cache.shape[2]
+    segments = segment_first_position.shape[0]
+    assert q.dtype == out.dtype == k_cache.dtype == v_cache.dtype == torch.bfloat16
+    assert q.is_contiguous() and out.is_contiguous() and k_cache.is_contiguous() and v_cache.is_contiguous()
+    assert v_cache.shape == k_cache.shape and k_cache.shape[3] == head_dim and out.numel() == tokens * n_q * head_dim
+    assert block_tables.dtype == torch.int32 and block_tables.stride(1) == 1 and segment_start.shape[0] == segments + 1
+    assert head_bias.dtype == torch.float32 and head_bias.shape == (n_q,)
+    scratch, counters = _attention_tc_scratch(q.device)
+    check(library.load().lse_attention_sigmoid_tc(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), out.data_ptr(),
+                                                  block_tables.data_ptr(), block_tables.stride(0), segment_start.data_ptr(),
+                                                  segment_first_position.data_ptr(), segments, tokens, pages, n_q, n_kv,
+                                                  head_dim, page_size, float(scale), head_bias.data_ptr(), float(cap),
+                                                  _ptr(scratch), _ptr(counters), counters.shape[0], _stream()),
+          "attention_sigmoid_tc")
+    return out
+
+
 def attention_scored_mma_supported(dk: int, dv: int, n_q: int, n_kv: int, dtype: torch.dtype) -> bool:
     """Whether the tensor-core form of :func:`attention_scored` takes this shape (bfloat16; keys and values of one
     size, 32, 48, 64, 96 or 128; at most 64 query heads a group)."""

@@ -271,8 +271,16 @@ class HeadNormRotaryAttention(BranchMixer):
         dk, dv = int(params["dim"]), int(params["vdim"])
         return PagedKV(int(params["kv_heads"]), dk, int(params.get("window", 0)), 0 if dv == dk else dv)
 
+    def _on_tcgen05(self, segment_counts, page_size=None) -> bool:
+        """Long prompt portions of the sigmoid-weighted form without a window run on the tcgen05 kernel."""
+        if not self.sigmoid or self.window > 0:
+            return False
+        if not prompt_shape_for_tcgen05(self.ctx.dtype, self.dk, self.dv, segment_counts):
+            return False
+        return page_size is None or ops.attention_tc_supported(self.dk, self.n_q, self.n_kv, page_size, self.ctx.dtype)
+
     def launch_signature(self, segment_counts):
-        return ()
+        return ("tcgen05",) if self._on_tcgen05(segment_counts) else ()
 
     def inner(self, proj, offset, step, cache, out, scale):
         pages = cache
@@ -282,10 +290,15 @@ class HeadNormRotaryAttention(BranchMixer):
                                     step.positions, self.freq, self.rot_factor, q, pages.keys, pages.values, self.n_q,
                                     self.n_kv, self.dk, self.dv, offset=offset)
         attended = torch.empty((tokens, self.n_q, self.dv), dtype=out.dtype, device=out.device)
-        ops.attention_scored(q, pages.keys, pages.values, attended, pages.block_tables, step.segment_of_token,
-                             step.positions, self.scale, segment_start=step.segment_start,
-                             segment_first_position=step.segment_first_position, window=self.window, cap=self.softcap,
-                             head_bias=self.head_bias)
+        if (not step.decode_only and step.segments
+                and self._on_tcgen05([segment.count for segment in step.segments], pages.keys.shape[2])):
+            ops.attention_sigmoid_tc(q, pages.keys, pages.values, attended, pages.block_tables, step.segment_start,
+                                     step.segment_first_position, self.scale, self.head_bias, self.softcap)
+        else:
+            ops.attention_scored(q, pages.keys, pages.values, attended, pages.block_tables, step.segment_of_token,
+                                 step.positions, self.scale, segment_start=step.segment_start,
+                                 segment_first_position=step.segment_first_position, window=self.window, cap=self.softcap,
+                                 head_bias=self.head_bias)
         ops.head_gate_scale(attended, None, out, scale, step.segment_of_token)
 
 

@@ -76,6 +76,13 @@ CONFIGS = {
     # every kind, and two layers that run a second time with the first run's tensors and a cache of their own
     "all_kinds": model([_FIRST, _SECOND, memory(), again(_FIRST, 0), sigmoid_attention(mlp=dense()), again(_SECOND, 1),
                         memory(heads=2, dim=64, vdim=16, mlp=moe(experts=8, top=4, count=4, keep=3))], width=80),
+    # head sizes that the tensor-core kernels take in bfloat16 (the windowed attention and single tokens on mma.sync, long
+    # prompt portions of the sigmoid-weighted attention on tcgen05)
+    "tensor_core_sizes": model([side_by_side(heads=4, kv_heads=2, dim=64, vdim=64, window=100, rot_dims=32, ssm_heads=4, ssm_vdim=32,
+                                             state=64),
+                                sigmoid_attention(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=64),
+                                memory(heads=2, dim=64, vdim=64),
+                                sigmoid_attention(heads=2, kv_heads=1, dim=128, vdim=128, rot_dims=64, mlp=dense())], width=128),
     # values that many models make equal or one: one head, one key/value head per query head, a window of one token and
     # a window wider than any prompt, every dimension rotated, a stretch factor of one, branches unscaled, one group and
     # a group per head, one norm part, one tap, one state row, tau one, one expert chosen, groups that shut nothing out,
@@ -222,12 +229,13 @@ def test_portions_of_changing_size(name, dtype):
 def test_a_long_prompt_is_scanned_in_chunks_and_in_portions_alike():
     """A prompt long enough for the chunked form of the scans (chunks side by side, a carry between them), whole and in
     portions that cut chunks anywhere."""
-    for name in ("all_kinds", "memory_only", "odd_sizes"):
+    for name, dtype in (("all_kinds", "float32"), ("memory_only", "float32"), ("odd_sizes", "float32"),
+                        ("tensor_core_sizes", "bfloat16"), ("tensor_core_sizes", "float32")):
         requests = some_requests(name, [413], seed=13)
-        whole = replay(name, "float32", helpers.trace_whole(requests), 448)
-        compare(name, "float32", requests, whole, "long whole")
-        cut = replay(name, "float32", helpers.trace_portions(requests, (130, 1, 199, 65, 2)), 448)
-        compare(name, "float32", requests, cut, "long in portions")
+        whole = replay(name, dtype, helpers.trace_whole(requests), 448)
+        compare(name, dtype, requests, whole, "long whole")
+        cut = replay(name, dtype, helpers.trace_portions(requests, (130, 1, 199, 65, 2)), 448)
+        compare(name, dtype, requests, cut, "long in portions")
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -412,6 +420,49 @@ def test_sigmoid_weights_are_not_normalised_and_find_a_far_key(dtype, sizes):
             limit = 3e-5 if dtype == torch.float32 else 3e-2
             error = (got.double() - want).abs()
             assert float(error.max()) <= limit * max(1.0, float(want.abs().max())), (special, len(cuts))
+
+
+@pytest.mark.parametrize("sizes", [(6, 2, 64, 64), (4, 1, 128, 128)])
+def test_sigmoid_weights_on_the_tcgen05_kernel(sizes):
+    """Long prompt portions on the 5th-generation tensor cores: three requests in a step (portions of 128 rows and more
+    behind prefixes of several lengths), a cap and none, against the plain weights; the kernel reports no wait that gave up."""
+    from llm_serving_engine_b200.kernels import ops
+
+    torch.manual_seed(13)
+    (n_q, n_kv, dk, dv), page = sizes, 16
+    scale = 2.0 / dk ** 0.5
+    head_bias = torch.linspace(-5.0, 0.5, n_q)
+    lengths, firsts = [300, 129, 700], [0, 40, 333]        # rows of the step, keys before them
+    for cap in (3.0, 0.0):
+        pool = sum(-(-(first + count) // page) for first, count in zip(firsts, lengths)) + 3
+        keys = torch.full((pool, n_kv, page, dk), float("nan"), dtype=torch.bfloat16, device="cuda")
+        values = torch.full((pool, n_kv, page, dv), float("nan"), dtype=torch.bfloat16, device="cuda")
+        order = torch.randperm(pool, generator=torch.Generator().manual_seed(5)).to(torch.int32)
+        width = max(-(-(first + count) // page) for first, count in zip(firsts, lengths))
+        tables = torch.zeros(len(lengths), width, dtype=torch.int32)
+        rows, wants, used = [], [], 0
+        for index, (first, count) in enumerate(zip(firsts, lengths)):
+            total = first + count
+            q, k, v = (torch.randn(total, n, d).to(torch.bfloat16).float() for n, d in ((n_q, dk), (n_kv, dk), (n_kv, dv)))
+            k[3, 0] = 4.0 * q[total - 1, 0]
+            v[3, 0] = 9.0
+            pages = -(-total // page)
+            tables[index, :pages] = order[used:used + pages]
+            places = torch.arange(total)
+            where, offset = order[used + places // page].long().cuda(), (places % page).cuda()
+            keys[where, :, offset] = k.to(torch.bfloat16).cuda()
+            values[where, :, offset] = v.to(torch.bfloat16).cuda()
+            used += pages
+            rows.append(q[first:])
+            wants.append(_plain_attention(q, k, v, scale, cap=cap, head_bias=head_bias)[first:])
+        step = _step(lengths, firsts)
+        out = torch.empty(sum(lengths), n_q, dv, dtype=torch.bfloat16, device="cuda")
+        ops.attention_sigmoid_tc(torch.cat(rows).to(torch.bfloat16).cuda().contiguous(), keys, values, out, tables.cuda(),
+                                 step.segment_start, step.segment_first_position, scale, head_bias.cuda(), cap)
+        assert ops.attention_tc_status() == 0
+        want = torch.cat(wants)
+        error = (out.float().cpu().double() - want).abs()
+        assert float(error.max()) <= 3e-2 * max(1.0, float(want.abs().max())), (cap, int(error.amax((1, 2)).argmax()))
 
 
 def test_heads_are_normed_one_by_one_then_rotated_far_from_the_start():

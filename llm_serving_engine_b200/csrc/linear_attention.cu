@@ -80,7 +80,7 @@ sigmoid_power_kernel(const TD* __restrict__ proj, int n_partials, long long part
 // with act the SiLU (gate_act 1) or the sigmoid (0); g: columns g_off .. of proj.  A block owns one part of one row
 // (grid: rows x parts); a thread keeps up to GGN_KEPT of the part's values (and gates) between the sum and the write.
 constexpr int GGN_KEPT = 8;
-template <typename TD, typename TO>
+template <typename TD, typename TO, bool SINGLE>
 __global__ void __launch_bounds__(256)
 gated_group_rmsnorm_kernel(const float* __restrict__ o, const TD* __restrict__ proj, int n_partials,
                            long long partial_stride, long long ld, int g_off, const TO* __restrict__ xsrc,
@@ -96,25 +96,36 @@ gated_group_rmsnorm_kernel(const float* __restrict__ o, const TD* __restrict__ p
   const int width = n / groups, lo = part * width;
   const float* row = o + (size_t)t * n;
   const TD* g = proj + (size_t)t * ld + g_off;
-  auto gate = [&](int i) {
-    const float z = la_load(g + i, n_partials, partial_stride);
+  auto act = [&](float z) {
     const float sg = 1.f / (1.f + expf(-z));
     return gate_act == 1 ? z * sg : sg;
   };
+  auto gate = [&](int i) { return act(SINGLE ? to_f32<TD>(g[i]) : la_load(g + i, n_partials, partial_stride)); };
   auto plain = [&](int i) {
     float a = row[i];
     if (skip) a = fmaf(skip[i / head_width], to_f32<TO>(xsrc[(size_t)t * x_ld + x_off + i]), a);
     return a;
   };
-  float kept[GGN_KEPT], gates[GGN_KEPT];
+  float kept[GGN_KEPT], gates[GGN_KEPT], side[GGN_KEPT];
   float sq = 0.f;
+  const TO* xrow = skip ? xsrc + (size_t)t * x_ld + x_off : nullptr;
+#pragma unroll
+  for (int k = 0; k < GGN_KEPT; ++k) {     // every load of the thread first, so that they travel together
+    const int i = lo + threadIdx.x + k * blockDim.x;
+    kept[k] = gates[k] = side[k] = 0.f;
+    if (i < lo + width) {
+      gates[k] = SINGLE ? to_f32<TD>(g[i]) : la_load(g + i, n_partials, partial_stride);
+      kept[k] = row[i];
+      if (skip) side[k] = to_f32<TO>(xrow[i]);
+    }
+  }
 #pragma unroll
   for (int k = 0; k < GGN_KEPT; ++k) {
     const int i = lo + threadIdx.x + k * blockDim.x;
-    kept[k] = gates[k] = 0.f;
     if (i < lo + width) {
-      gates[k] = gate(i);
-      kept[k] = gate_first ? plain(i) * gates[k] : plain(i);
+      gates[k] = act(gates[k]);
+      if (skip) kept[k] = fmaf(skip[i / head_width], side[k], kept[k]);
+      if (gate_first) kept[k] *= gates[k];
       sq = fmaf(kept[k], kept[k], sq);
     }
   }
@@ -137,6 +148,63 @@ gated_group_rmsnorm_kernel(const float* __restrict__ o, const TD* __restrict__ p
     float y = ((gate_first ? plain(i) * gi : plain(i)) * inv) * weight[i % weight_len];
     if (!gate_first) y *= gi;
     out[(size_t)t * out_ld + i] = from_f32<TO>(y * scale);
+  }
+}
+// The same for narrow parts (up to 32 * GGN_WARP_KEPT columns): a warp owns a part of a row, eight parts a block, no
+// barrier; the part's values and gates stay in registers.
+constexpr int GGN_WARP_KEPT = 16;
+template <typename TD, typename TO, bool SINGLE>
+__global__ void __launch_bounds__(256)
+gated_group_rmsnorm_warp_kernel(const float* __restrict__ o, const TD* __restrict__ proj, int n_partials,
+                                long long partial_stride, long long ld, int g_off, const TO* __restrict__ xsrc,
+                                long long x_ld, int x_off, const float* __restrict__ skip, int head_width,
+                                const float* __restrict__ weight, int weight_len, TO* __restrict__ out, long long out_ld,
+                                int tokens, int n, int groups, float eps, float scale, int gate_first, int gate_act,
+                                const int* __restrict__ segment_of_token) {
+  pdl_launch_dependents();
+  pdl_wait();
+  const long long item = (blockIdx.x * (long long)blockDim.x + threadIdx.x) >> 5;
+  const int lane = threadIdx.x & 31;
+  if (item >= (long long)tokens * groups) return;
+  const int t = (int)(item / groups), part = (int)(item % groups);
+  if (segment_of_token && segment_of_token[t] < 0) return;
+  const int width = n / groups, lo = part * width;
+  const float* row = o + (size_t)t * n + lo;
+  const TD* g = proj + (size_t)t * ld + g_off + lo;
+  const TO* x = skip ? xsrc + (size_t)t * x_ld + x_off + lo : nullptr;
+  float kept[GGN_WARP_KEPT], gates[GGN_WARP_KEPT];
+  float sq = 0.f;
+#pragma unroll
+  for (int k = 0; k < GGN_WARP_KEPT; ++k) {     // every load of the lane first, so that they travel together
+    const int c = lane + 32 * k;
+    kept[k] = gates[k] = 0.f;
+    if (c < width) {
+      gates[k] = SINGLE ? to_f32<TD>(g[c]) : la_load(g + c, n_partials, partial_stride);
+      kept[k] = row[c];
+    }
+  }
+#pragma unroll
+  for (int k = 0; k < GGN_WARP_KEPT; ++k) {
+    const int c = lane + 32 * k;
+    if (c < width) {
+      const float z = gates[k];
+      const float sg = 1.f / (1.f + expf(-z));
+      gates[k] = gate_act == 1 ? z * sg : sg;
+      if (skip) kept[k] = fmaf(skip[(lo + c) / head_width], to_f32<TO>(x[c]), kept[k]);
+      if (gate_first) kept[k] *= gates[k];
+      sq = fmaf(kept[k], kept[k], sq);
+    }
+  }
+  const float inv = 1.0f / sqrtf(warp_sum(sq) / (float)width + eps);
+  const int w0 = lo % weight_len;      // the part's first weight; parts are whole multiples or whole fractions of the weight
+#pragma unroll
+  for (int k = 0; k < GGN_WARP_KEPT; ++k) {
+    const int c = lane + 32 * k;
+    if (c < width) {
+      float y = (kept[k] * inv) * weight[(w0 + c) % weight_len];
+      if (!gate_first) y *= gates[k];
+      out[(size_t)t * out_ld + lo + c] = from_f32<TO>(y * scale);
+    }
   }
 }
 }  // namespace
@@ -222,15 +290,31 @@ extern "C" int lse_gated_group_rmsnorm(const float* o, const void* proj, int pro
   const int width = n / groups;
   const int threads = width >= 1024 ? 256 : (width >= 256 ? 128 : (width > 32 ? 64 : 32));
   const dim3 grid(tokens, groups);
+  const bool narrow = width <= 32 * GGN_WARP_KEPT;
+  const long long warp_blocks = ((long long)tokens * groups + 7) / 8;
+  if (narrow && warp_blocks > 0x7fffffffLL) return LSE_ERR_TOO_LARGE;
+#define LSE_GGN_FORM(TD, TO, SINGLE)                                                                                 \
+  if ((n_partials == 1) == SINGLE) {                                                                                 \
+    if (narrow)                                                                                                      \
+      lse_launch(gated_group_rmsnorm_warp_kernel<TD, TO, SINGLE>, (unsigned)warp_blocks, 256, 0, stream, o,           \
+                 (const TD*)proj, n_partials, partial_stride, ld, g_off, (const TO*)xsrc, x_ld, x_off, skip,          \
+                 head_width, weight, weight_len, (TO*)out, out_ld, tokens, n, groups, eps, scale, gate_first,         \
+                 gate_act, segment_of_token);                                                                        \
+    else                                                                                                             \
+      lse_launch(gated_group_rmsnorm_kernel<TD, TO, SINGLE>, grid, threads, 0, stream, o, (const TD*)proj,            \
+                 n_partials, partial_stride, ld, g_off, (const TO*)xsrc, x_ld, x_off, skip, head_width, weight,       \
+                 weight_len, (TO*)out, out_ld, n, groups, eps, scale, gate_first, gate_act, segment_of_token);        \
+  }
 #define LSE_GGN_CASE(TD, TO)                                                                                         \
-  lse_launch(gated_group_rmsnorm_kernel<TD, TO>, grid, threads, 0, stream, o, (const TD*)proj, n_partials,            \
-             partial_stride, ld, g_off, (const TO*)xsrc, x_ld, x_off, skip, head_width, weight, weight_len, (TO*)out, \
-             out_ld, n, groups, eps, scale, gate_first, gate_act, segment_of_token);
+  {                                                                                                                  \
+  LSE_GGN_FORM(TD, TO, true) else LSE_GGN_FORM(TD, TO, false)                                                        \
+  }
   const bool d32 = proj_dtype == LSE_DTYPE_F32, o32 = out_dtype == LSE_DTYPE_F32;
   if (d32 && o32) LSE_GGN_CASE(float, float)
   else if (d32 && !o32) LSE_GGN_CASE(float, __nv_bfloat16)
   else if (!d32 && o32) LSE_GGN_CASE(__nv_bfloat16, float)
   else LSE_GGN_CASE(__nv_bfloat16, __nv_bfloat16)
 #undef LSE_GGN_CASE
+#undef LSE_GGN_FORM
   LSE_LAUNCH_CHECK();
 }

@@ -32,7 +32,7 @@ MIXER_TYPES = ("parallel", "attention", "gla")
 _ATTENTION_KEYS = ("heads", "kv_heads", "dim", "vdim", "scale")
 _MIXER_KEYS = {
     "parallel": ("left", "right", "left_scale", "right_scale"),
-    "attention": _ATTENTION_KEYS + ("softcap",),
+    "attention": _ATTENTION_KEYS,
     "gla": ("heads", "dim", "vdim", "tau"),
 }
 _RIGHT_KEYS = ("heads", "vdim", "state", "groups", "conv")

@@ -25,7 +25,7 @@ def _attention_params(mixer: dict, eps: float, **more) -> dict:
 def _mixer_spec(kind: str, mixer: dict, eps: float) -> PartSpec:
     if kind == "attention":
         return PartSpec("head_norm_rotary_attention", _attention_params(
-            mixer, eps, bias=False, weights="sigmoid", softcap=float(mixer["softcap"]),
+            mixer, eps, bias=False, weights="sigmoid", softcap=float(mixer.get("softcap", 0.0)),
             window=int((mixer.get("mask") or {}).get("size", 0))))
     if kind == "gla":
         return PartSpec("channel_decay_linear_attention", {

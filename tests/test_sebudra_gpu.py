@@ -77,10 +77,11 @@ CONFIGS = {
     "all_kinds": model([_FIRST, _SECOND, memory(), again(_FIRST, 0), sigmoid_attention(mlp=dense()), again(_SECOND, 1),
                         memory(heads=2, dim=64, vdim=16, mlp=moe(experts=8, top=4, count=4, keep=3))], width=80),
     # head sizes that the tensor-core kernels take in bfloat16 (the windowed attention and single tokens on mma.sync, long
-    # prompt portions of the sigmoid-weighted attention on tcgen05)
+    # prompt portions of the sigmoid-weighted attention on tcgen05); no router, so that no row of a long bfloat16 run
+    # rests on a close call between two experts
     "tensor_core_sizes": model([side_by_side(heads=4, kv_heads=2, dim=64, vdim=64, window=100, rot_dims=32, ssm_heads=4, ssm_vdim=32,
                                              state=64),
-                                sigmoid_attention(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=64),
+                                sigmoid_attention(heads=4, kv_heads=2, dim=64, vdim=64, rot_dims=64, mlp=dense(ff=120)),
                                 memory(heads=2, dim=64, vdim=64),
                                 sigmoid_attention(heads=2, kv_heads=1, dim=128, vdim=128, rot_dims=64, mlp=dense())], width=128),
     # values that many models make equal or one: one head, one key/value head per query head, a window of one token and
@@ -248,6 +249,30 @@ def test_mixed_batches_reuse_pages_and_slots(dtype, page):
     steps, peak = helpers.trace_mixed(requests, seed=3, max_live=4)
     got = replay("all_kinds", dtype, steps, peak, page=page)
     compare("all_kinds", dtype, requests, got, "mixed")
+
+
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_long_portions_beside_single_tokens_on_the_tensor_cores(dtype):
+    """Steps in which a portion of 128 rows and more stands beside other portions and single decoded tokens, with head
+    sizes that the tensor-core kernels take: in bfloat16 the sigmoid-weighted layers then run on tcgen05 (a single token
+    takes a tile of its own there) and the windowed ones on mma.sync; pages and slots are used again by a fourth request."""
+    name = "tensor_core_sizes"
+    requests = some_requests(name, [156, 150, 270, 140], seed=21)
+    a, b, c, d = (requests[f"r{index}"] for index in range(4))
+
+    def entry(rid, tokens, first, count):
+        return {"id": rid, "tokens": tokens[first:first + count], "want": list(range(count))}
+
+    steps = [
+        {"step": 0, "entries": [entry("r0", a, 0, 150), entry("r1", b, 0, 3)], "end": []},
+        {"step": 1, "entries": [entry("r0", a, 150, 1), entry("r1", b, 3, 140), entry("r2", c, 0, 130)], "end": []},
+        {"step": 2, "entries": [entry("r0", a, 151, 1), entry("r1", b, 143, 1), entry("r2", c, 130, 135)], "end": []},
+        {"step": 3, "entries": [entry("r0", a, 152, 4), entry("r1", b, 144, 6), entry("r2", c, 265, 1)], "end": ["r0", "r1"]},
+        {"step": 4, "entries": [entry("r2", c, 266, 1), entry("r3", d, 0, 128)], "end": []},
+        {"step": 5, "entries": [entry("r2", c, 267, 3), entry("r3", d, 128, 12)], "end": ["r2", "r3"]},
+    ]
+    got = replay(name, dtype, steps, 640)
+    compare(name, dtype, requests, got, "long portions beside single tokens")
 
 
 def test_a_batch_gives_what_each_request_gives_alone():

@@ -388,7 +388,7 @@ def _plain_attention(q, k, v, scale, window=0, cap=0.0, head_bias=None):
 
 
 # head sizes that the general kernel takes (keys and values of different sizes) and that the tensor-core kernel takes in bfloat16
-_HEAD_SIZES = [(4, 2, 24, 40), (4, 2, 64, 64), (6, 2, 48, 48), (8, 1, 128, 128)]
+_HEAD_SIZES = [(4, 2, 24, 40), (4, 2, 64, 64), (6, 2, 48, 48), (8, 1, 128, 128), (4, 2, 96, 96), (3, 1, 32, 32)]
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -421,7 +421,7 @@ def test_a_window_ends_where_it_should(dtype, window, sizes):
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
-@pytest.mark.parametrize("sizes", [(6, 2, 16, 24), (6, 2, 64, 64), (6, 3, 32, 32), (6, 1, 128, 128)])
+@pytest.mark.parametrize("sizes", [(6, 2, 16, 24), (6, 2, 64, 64), (6, 3, 32, 32), (6, 1, 128, 128), (6, 3, 96, 96), (6, 2, 48, 48)])
 def test_sigmoid_weights_are_not_normalised_and_find_a_far_key(dtype, sizes):
     """Weights sigmoid(capped score + a number per head): the output grows with the number of keys (a softmax's would
     not), the cap bounds what one key can weigh, and one far key with a large score and a large value shows at the

@@ -575,7 +575,7 @@ TUFEVIK_SIZES = {
 # matrix memory with channel decays, side by side, sigmoid attention, matrix memory]; attention heads of 128 in groups of
 # eight (the windowed one over 512 keys, half of a head rotated with stretched frequencies); a state-space scan of as
 # many channels as the model is wide in heads of 64 with 128 state rows and two groups, four taps; a matrix memory with
-# heads of 64 key channels and 128 values and a decay map of rank 16; dense feed-forwards and mixtures of eight ungated
+# heads of 64 key channels and 128 values and a decay map of rank 32; dense feed-forwards and mixtures of eight ungated
 # experts in four groups (two kept) of half the dense size of which a token uses two, beside a shared expert of the same
 # size, so that a token's feed-forward work equals the gated dense layer's.  The closest existing model is Tufevik (an
 # attention and a scan side by side, a matrix memory, mixtures of experts): it is measured beside it at equal size.
@@ -615,16 +615,16 @@ def tufevik_config(width: int, heads: int, ff: int, vocab: int = 32768, context:
 
 def sebudra_config(width: int, heads: int, ff: int, vocab: int = 32768, context: int = 4096) -> dict:
     dense = {"kind": "dense", "ff": ff, "limit": 7.0}
-    mixture = {"kind": "moe", "router": {"experts": 8, "top": 2, "scale": 1.5, "groups": {"count": 4, "keep": 2}},
+    mixture = {"kind": "moe", "router": {"experts": 8, "top": 2, "scale": 2.5, "groups": {"count": 4, "keep": 2}},
                "expert": {"ff": ff // 2}, "shared": {"ff": ff // 2}}
     kv_heads = max(2, heads // 8)
     left = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "mask": {"size": 512},
-            "rot": {"base": 500000.0, "dims": 64, "scaling": {"factor": 4.0, "original": 2048, "fast": 16.0, "slow": 1.0}}}
+            "rot": {"base": 1000000.0, "dims": 64, "scaling": {"factor": 8.0, "original": 2048, "fast": 16.0, "slow": 1.0}}}
     right = {"heads": width // 64, "vdim": 64, "state": 128, "groups": 2, "conv": 4, "norm_groups": 2}
     side_by_side = {"left": left, "right": right, "left_scale": 0.5, "right_scale": 0.5}
-    attention = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 30.0,
-                 "rot": {"base": 250000.0, "dims": 128}}
-    memory = {"heads": heads, "dim": 64, "vdim": 128, "tau": 16.0, "rank": 16}
+    attention = {"heads": heads, "kv_heads": kv_heads, "dim": 128, "vdim": 128, "scale": 128 ** -0.5, "softcap": 50.0,
+                 "rot": {"base": 1000000.0, "dims": 128}}
+    memory = {"heads": heads, "dim": 64, "vdim": 128, "tau": 8.0, "rank": 32}
     layers = [{"type": "parallel", "mixer": side_by_side, "mlp": dense}, {"type": "attention", "mixer": attention, "mlp": mixture},
               {"type": "gla", "mixer": memory, "mlp": mixture}, {"type": "parallel", "mixer": side_by_side, "mlp": dense},
               {"type": "attention", "mixer": attention, "mlp": dense}, {"type": "gla", "mixer": memory, "mlp": mixture}]

@@ -82,7 +82,7 @@ def _sebudra_stand_in(vocab_size: int) -> dict:
     """A small model of the Sebudra design: a layer with a windowed attention and a state-space scan side by side over a
     dense feed-forward, a sigmoid-weighted attention over a mixture of experts, a matrix memory with a decay per key
     channel, and the first layer once more with its tensors and a cache of its own."""
-    mlp = {"kind": "moe", "router": {"experts": 6, "top": 2, "scale": 1.5, "groups": {"count": 3, "keep": 2}},
+    mlp = {"kind": "moe", "router": {"experts": 6, "top": 2, "scale": 2.0, "groups": {"count": 3, "keep": 2}},
            "expert": {"ff": 96}, "shared": {"ff": 128}}
     dense = {"kind": "dense", "ff": 352, "limit": 3.0}
     left = {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 32 ** -0.5, "mask": {"size": 48},
@@ -96,7 +96,7 @@ def _sebudra_stand_in(vocab_size: int) -> dict:
                        {"type": "attention", "mlp": mlp,
                         "mixer": {"heads": 4, "kv_heads": 2, "dim": 32, "vdim": 32, "scale": 32 ** -0.5, "softcap": 20.0,
                                   "rot": {"base": 10000.0, "dims": 32}}},
-                       {"type": "gla", "mlp": mlp, "mixer": {"heads": 4, "dim": 32, "vdim": 32, "tau": 16.0, "rank": 16}},
+                       {"type": "gla", "mlp": mlp, "mixer": {"heads": 4, "dim": 32, "vdim": 32, "tau": 8.0, "rank": 8}},
                        dict(first, weights_of=0)]}
 
 

@@ -349,7 +349,7 @@ def tensor_shapes(cfg: dict) -> dict[str, tuple]:
         if kind == "gla":
             q = p + "mix."
             heads, d, e = int(m["heads"]), int(m["dim"]), int(m["vdim"])
-            rank = int(m.get("rank", 16))
+            rank = int(m["rank"])       # no key of the design's own: a model written here names it
             out[q + "q"] = ((heads * d, width), "matrix")
             out[q + "k"] = ((heads * d, width), "matrix")
             out[q + "v"] = ((heads * e, width), "matrix")

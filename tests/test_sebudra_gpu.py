@@ -320,6 +320,105 @@ def test_greedy_generation_through_the_engine_and_its_scheduler():
             assert int(row.argmax()) == token, f"token {index} of a {len(prompt)}-token prompt"
 
 
+# ------------------------------------------------------------------ architectures drawn at random
+def _divisors(n):
+    return [d for d in range(1, n + 1) if n % d == 0]
+
+
+def _drawn_attention(rng, windowed):
+    kv_heads, group = rng.choice([1, 2, 3]), rng.choice([1, 2, 3, 4])
+    dim = rng.choice([16, 24, 32, 48, 64, 96, 128])
+    vdim = dim if rng.random() < 0.5 else rng.choice([8, 16, 40, 48, 64])
+    rot = {"base": rng.choice([100.0, 10000.0, 1000000.0]),
+           "dims": rng.choice([d for d in (2, 4, 8, 16, dim // 2, dim) if d <= dim and d % 2 == 0])}
+    if rng.random() < (0.8 if windowed else 0.3):
+        rot["scaling"] = {"factor": rng.choice([1.0, 2.0, 3.0, 8.0]), "original": rng.choice([32, 64, 256]),
+                          "fast": rng.choice([4.0, 8.0, 16.0]), "slow": rng.choice([0.5, 1.0])}
+    mixer = {"heads": kv_heads * group, "kv_heads": kv_heads, "dim": dim, "vdim": vdim,
+             "scale": rng.choice([1.0, 1.5, 2.0]) / dim ** 0.5, "rot": rot}
+    if windowed:
+        mixer["mask"] = {"size": rng.choice([1, 3, 16, 17, 33, 64, 100, 500])}
+    else:
+        mixer["softcap"] = rng.choice([1.0, 5.0, 20.0, 100.0])
+    return mixer
+
+
+def _drawn_feed_forward(rng):
+    draw = rng.random()
+    if draw < 0.15:
+        return None
+    if draw < 0.55:
+        return dense(ff=rng.choice([24, 50, 88, 128]), limit=rng.choice([0.7, 1.75, 7.0]))
+    experts = rng.choice([2, 4, 6, 8, 12])
+    if rng.random() < 0.7:
+        count = rng.choice(_divisors(experts))
+        keep = rng.randint(1, count)
+        top = rng.randint(1, keep * (experts // count))
+    else:
+        count, keep, top = 0, 0, rng.randint(1, experts)
+    return moe(experts=experts, top=top, ff=rng.choice([8, 18, 40, 64]), count=count, keep=keep,
+               scale=rng.choice([1.0, 1.25, 2.5]), shared=rng.choice([0, 8, 24, 48]))
+
+
+def _drawn_layer(rng):
+    kind = rng.choice(["parallel", "attention", "gla"])
+    if kind == "parallel":
+        heads, vdim = rng.choice([1, 2, 4, 6, 8]), rng.choice([4, 8, 12, 48, 64])
+        right = {"heads": heads, "vdim": vdim, "state": rng.choice([1, 2, 8, 16, 32, 64, 128]), "groups": rng.choice(_divisors(heads)),
+                 "conv": rng.choice([1, 2, 3, 4, 5]), "norm_groups": rng.choice([d for d in _divisors(heads * vdim) if d <= 8])}
+        mixer = {"left": _drawn_attention(rng, True), "right": right, "left_scale": rng.choice([0.3, 1.0, 1.7]),
+                 "right_scale": rng.choice([0.4, 1.0, 1.3])}
+    elif kind == "attention":
+        mixer = _drawn_attention(rng, False)
+    else:
+        mixer = {"heads": rng.choice([1, 2, 3, 6]), "dim": rng.choice([8, 16, 32, 64, 96]), "vdim": rng.choice([8, 24, 64, 100]),
+                 "tau": rng.choice([1.0, 4.0, 8.0]), "rank": rng.choice([1, 4, 8])}
+    return {"type": kind, "mixer": mixer, "mlp": _drawn_feed_forward(rng)}
+
+
+def _drawn_model(rng):
+    """Two to five layers of any kinds in any order with sizes drawn one by one, and up to two more that run an earlier
+    layer again on its tensors."""
+    own = [_drawn_layer(rng) for _ in range(rng.randint(2, 5))]
+    layers = [(layer, None) for layer in own]
+    for _ in range(rng.randint(0, 2)):
+        source = rng.randrange(len(own))
+        place = rng.randint([index for index, (layer, of) in enumerate(layers) if layer is own[source] and of is None][0] + 1, len(layers))
+        layers.insert(place, (own[source], source))
+    entries = []
+    for layer, of in layers:
+        if of is None:
+            entries.append(layer)
+        else:     # the index of the source among all entries, which the insertions have moved
+            entries.append(again(layer, [index for index, (other, other_of) in enumerate(layers) if other is layer and other_of is None][0]))
+    return model(entries, width=rng.choice([48, 64, 96, 120, 256]), vocab=rng.choice([97, 300, 501]),
+                 embed_scale=rng.choice([1.0, 3.0, 9.0]), eps=rng.choice([1e-5, 1e-6]))
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_architectures_drawn_at_random(seed):
+    """Kinds, order, sizes and constants drawn at random, four requests whole, in portions of drawn sizes, with decoded
+    tails and in mixed batches through four slots, in float32 against the plain implementation (a router's close call
+    would decide a bfloat16 row, so the draw is compared where rounding does not reach it)."""
+    rng = random.Random(1000 + seed)
+    config = _drawn_model(rng)
+    name = f"drawn_{seed}"
+    CONFIGS[name] = config
+    try:
+        requests = {f"r{index}": helpers.random_tokens(rng, config["vocab"], count)
+                    for index, count in enumerate([rng.randint(1, 40), rng.randint(100, 300), rng.randint(30, 150), rng.randint(2, 70)])}
+        sizes = tuple(rng.choice([1, 2, 3, 7, 16, 33, 64, 130]) for _ in range(6))
+        peak = helpers.max_tokens_for(requests)
+        compare(name, "float32", requests, replay(name, "float32", helpers.trace_whole(requests), peak), f"whole {config['layers']}")
+        compare(name, "float32", requests, replay(name, "float32", helpers.trace_portions(requests, sizes), peak), f"portions {sizes}")
+        compare(name, "float32", requests, replay(name, "float32", helpers.trace_tail_decode(requests, tail=20), peak), "tail decoded")
+        steps, live = helpers.trace_mixed(requests, seed=seed, max_live=4)
+        compare(name, "float32", requests, replay(name, "float32", steps, live), "mixed")
+    finally:
+        CONFIGS.pop(name, None)
+        _MODELS.pop(name, None)
+
+
 # ------------------------------------------------------------------ the mechanisms' kernels alone
 def _step(lengths, first_positions=None, slots=None):
     """The step's tensors that the kernels read, for requests of ``lengths`` rows laid one after the other."""
